@@ -1,0 +1,239 @@
+/*
+ * lmserve_kv.h — C ABI of the B200 (sm_100a) KV-cache data-movement library.
+ *
+ * The library replaces the GPU data path of LMServe's Python worker: the paged
+ * cache write, the copy-on-write block copy, the GPU<->pinned-host block swap
+ * and the prefill->decode block transfer.  LMServe itself has no C interface;
+ * each entry point below names the Python callable (path inside the LMServe
+ * source tree, file:line) whose device work it performs.
+ *
+ * Conventions shared by every entry point
+ *   - plain pointers and sizes only; nothing is allocated, owned or freed on
+ *     behalf of the caller unless the function name says so (lms_host_alloc,
+ *     lms_ipc_open);
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default
+ *     stream); work is enqueued asynchronously on it and the call returns
+ *     without synchronising;
+ *   - the CUDA device of the calling thread must be the device that owns the
+ *     (local) cache pointer;
+ *   - all byte strides, row sizes and chunk sizes must be multiples of 16 and
+ *     all data pointers 16-byte aligned (LMS_ERR_ALIGN otherwise);
+ *   - the return value is LMS_OK (0) or a negative lms_status; no exceptions,
+ *     no abort, no device-side trap.
+ *
+ * Paged layout (runtime/worker/llm_worker/model_worker.py:221-228): one GPU
+ * tensor [num_layers, num_blocks, 2, block_size, num_kv_heads, head_dim], K in
+ * plane 0 and V in plane 1 of every block.  A "row" is one token's K (or V),
+ * row_bytes = num_kv_heads*head_dim*elem.  A "chunk" is one (layer, block) =
+ * 2*block_size*row_bytes contiguous bytes.  The pinned host pool is
+ * block-major, [num_host_blocks, num_layers, chunk]
+ * (runtime/worker/llm_worker/kv_worker.py:123-130).
+ */
+#ifndef LMSERVE_KV_H_
+#define LMSERVE_KV_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LMS_VERSION 100 /* major*10000 + minor*100 + patch */
+
+typedef enum lms_status {
+  LMS_OK = 0,
+  LMS_ERR_NULL = -1,      /* a required pointer is NULL                      */
+  LMS_ERR_ALIGN = -2,     /* pointer / stride / size not a multiple of 16    */
+  LMS_ERR_RANGE = -3,     /* negative count, empty layer range, bad enum ... */
+  LMS_ERR_CUDA = -4,      /* a CUDA runtime call failed (see lms_last_cuda_error) */
+  LMS_ERR_INDEX = -5,     /* debug checks: an index was out of range         */
+  LMS_ERR_PEER = -6,      /* peer access between the two devices unavailable */
+  LMS_ERR_UNSUPPORTED = -7
+} lms_status;
+
+/* Direction of lms_swap_blocks. */
+#define LMS_SWAP_OUT 0 /* GPU  -> host (kv_worker.py "save")  */
+#define LMS_SWAP_IN 1  /* host -> GPU  (kv_worker.py "load")  */
+
+/* Tunables for lms_set_tuning (values <= 0 restore the built-in choice). */
+#define LMS_TUNE_WRITE_VARIANT 1 /* 0 = 16-byte ld/st, 1 = 32-byte ld/st, 2 = bulk-copy (TMA) rows */
+#define LMS_TUNE_WRITE_TILE_BYTES 2 /* payload bytes read per CTA of the cache write */
+#define LMS_TUNE_COPY_VARIANT 3  /* 0 = 16-byte ld/st, 1 = 32-byte ld/st, 2 = bulk-copy (TMA) */
+#define LMS_TUNE_COPY_CTAS_PER_SM 4
+#define LMS_TUNE_SWAP_OUT_CTAS 5 /* total CTAs of the GPU->host kernel */
+#define LMS_TUNE_SWAP_IN_CTAS 6  /* total CTAs of the host->GPU kernel */
+#define LMS_TUNE_XFER_CTAS_PER_SM 7
+#define LMS_TUNE_XFER_VARIANT 8  /* 0 = 16-byte ld/st, 1 = 32-byte, 2 = bulk-copy */
+#define LMS_TUNE__COUNT 9
+
+/* Library version (LMS_VERSION of the build). */
+int lms_version(void);
+
+/* Static, NUL-terminated description of a status code. */
+const char* lms_strerror(int status);
+
+/* Text of the last CUDA error seen by the calling thread inside this library. */
+const char* lms_last_cuda_error(void);
+
+/* Overrides a launch tunable for every later call in this process. */
+int lms_set_tuning(int key, int value);
+int lms_get_tuning(int key);
+
+/*
+ * Debug checks.  When enabled, every kernel verifies each slot / block index
+ * against the bounds the caller passed (num_slots, num_*_blocks > 0), skips the
+ * offending access instead of performing it, and records the first offender in
+ * a per-device error record: 32 bytes of device memory owned by the library,
+ * allocated with cudaMalloc by the first call of any entry point on a device
+ * (so make that first call outside stream capture).
+ * lms_check_device_errors synchronises `stream`, reads the record back, clears
+ * it, and returns LMS_ERR_INDEX if a kernel reported an index; `index` / `value`
+ * (optional) receive the position in the index table and the bad value.
+ */
+int lms_set_debug_checks(int enable);
+int lms_check_device_errors(void* stream, int64_t* index, int64_t* value);
+
+/*
+ * Paged cache write for one layer — replaces
+ *   fill_key_cache            runtime/worker/llm_worker/ops/cache_ops.py:39-59
+ *   fill_key_cache_kernel     runtime/worker/llm_worker/ops/triton/cache_kernels.py:39-58
+ * and the live per-layer call flashinfer.append_paged_kv_cache at
+ *   runtime/worker/llm_worker/models/layers/attention.py:76-85.
+ *
+ * For every token t with slot = slot_mapping[t] >= 0:
+ *   key_cache  [(slot / block_size) * block_stride + (slot % block_size) * slot_stride] <- key  [t]
+ *   value_cache[ same offset ]                                                         <- value[t]
+ * (row_bytes bytes each).  slot < 0 marks padding and is skipped.  Slots must be
+ * distinct.  With block_stride = block_size*slot_stride the caches are the flat
+ * [num_slots, H, D] arrays of fill_key_cache; with key_cache = &kv[layer][0][0],
+ * value_cache = &kv[layer][0][1] and block_stride = chunk bytes they are the
+ * interleaved per-layer cache that attention reads.
+ * num_slots is used by the debug checks only (0 = unknown).
+ */
+int lms_reshape_and_cache(const void* key, const void* value,
+                          int64_t key_token_stride, int64_t value_token_stride,
+                          void* key_cache, void* value_cache,
+                          int64_t block_stride, int64_t slot_stride,
+                          const int64_t* slot_mapping, int64_t num_tokens,
+                          int64_t row_bytes, int32_t block_size,
+                          int64_t num_slots, void* stream);
+
+/*
+ * The same write for num_layers layers in ONE launch (the per-layer loop of
+ * runtime/worker/llm_worker/models/llama.py:236-242 collapsed): layer l reads
+ * key + l*key_layer_stride, value + l*value_layer_stride and writes the caches
+ * at + l*cache_layer_stride.  slot_layer_stride is in elements; 0 shares one
+ * slot_mapping between all layers, as the reference's block tables do.
+ */
+int lms_reshape_and_cache_layers(const void* key, const void* value,
+                                 int64_t key_token_stride, int64_t value_token_stride,
+                                 int64_t key_layer_stride, int64_t value_layer_stride,
+                                 void* key_cache, void* value_cache,
+                                 int64_t cache_layer_stride,
+                                 int64_t block_stride, int64_t slot_stride,
+                                 const int64_t* slot_mapping, int64_t slot_layer_stride,
+                                 int64_t num_tokens, int32_t num_layers,
+                                 int64_t row_bytes, int32_t block_size,
+                                 int64_t num_slots, void* stream);
+
+/*
+ * Copy-on-write block copy — replaces
+ *   copy_blocks               runtime/worker/llm_worker/ops/cache_ops.py:8-36
+ *   copy_blocks_kernel        runtime/worker/llm_worker/ops/triton/cache_kernels.py:5-36
+ * For every pair p and every layer l:
+ *   kv[l*layer_stride + dst_p*block_stride ...] <- kv[l*layer_stride + src_p*block_stride ...]
+ * (chunk_bytes bytes).  `pairs` is a device array of n_pairs (src, dst) int64
+ * couples, 16-byte aligned.  Destinations must be distinct and no destination
+ * may also be a source in the same call.  num_blocks: debug checks only.
+ */
+int lms_copy_blocks(void* kv, int64_t layer_stride, int64_t block_stride,
+                    int64_t chunk_bytes, int32_t num_layers,
+                    const int64_t* pairs, int64_t n_pairs,
+                    int64_t num_blocks, void* stream);
+
+/*
+ * GPU <-> pinned-host block swap for layers [layer_begin, layer_end) — replaces
+ *   KVWorker._save_layer_kv_blocks_to_host   runtime/worker/llm_worker/kv_worker.py:213-227
+ *   KVWorker._load_layer_kv_blocks_from_host runtime/worker/llm_worker/kv_worker.py:197-211
+ * (one cuMemcpy{DtoH,HtoD}Async per (layer, block) there; one kernel here).
+ *   LMS_SWAP_OUT: host[dst_p][l] <- gpu[l][src_p]      LMS_SWAP_IN: gpu[l][dst_p] <- host[src_p][l]
+ * gpu chunk address  = gpu  + l*gpu_layer_stride  + block*gpu_block_stride
+ * host chunk address = host + block*host_block_stride + l*host_layer_stride
+ * `host` must be the DEVICE-visible address of page-locked, mapped host memory
+ * (lms_host_alloc / lms_host_register return it).  `pairs` (src, dst) int64
+ * couples must be readable by the GPU (device memory or mapped host memory).
+ * The layer range keeps the reference's layer-pipelined swap possible
+ * (kv_worker.py:249-295 records / waits one event per layer).
+ */
+int lms_swap_blocks(int direction, void* gpu, int64_t gpu_layer_stride,
+                    int64_t gpu_block_stride, void* host,
+                    int64_t host_block_stride, int64_t host_layer_stride,
+                    int64_t chunk_bytes, int32_t layer_begin, int32_t layer_end,
+                    const int64_t* pairs, int64_t n_pairs,
+                    int64_t num_gpu_blocks, int64_t num_host_blocks,
+                    void* stream);
+
+/*
+ * Prefill -> decode block transfer — replaces the three hops of
+ *   KVWorker.push_kv / _push_kv   runtime/worker/llm_worker/kv_worker.py:358-415
+ * (GPU -> host write-through, NIXL/UCX host -> host WRITE, host -> GPU fetch)
+ * with one kernel on the source GPU that reads local chunks and stores them
+ * into the destination GPU's cache over NVLink:
+ *   dst[l][dst_p] <- src[l][src_p]   for every pair p and layer l < num_layers.
+ * `dst` is the peer cache as mapped into this process (peer access enabled on
+ * a same-process pointer, or the result of lms_ipc_open).  Completion is
+ * ordered by `stream` like any kernel; there is no device-side handshake.
+ */
+int lms_transfer_blocks(const void* src, int64_t src_layer_stride,
+                        int64_t src_block_stride, void* dst,
+                        int64_t dst_layer_stride, int64_t dst_block_stride,
+                        int64_t chunk_bytes, int32_t num_layers,
+                        const int64_t* pairs, int64_t n_pairs,
+                        int64_t num_src_blocks, int64_t num_dst_blocks,
+                        void* stream);
+
+/* Enables peer access from the current device to `peer_device`
+ * (LMS_ERR_PEER when the two GPUs cannot reach each other). */
+int lms_peer_enable(int peer_device);
+
+/*
+ * Pinned host pool helpers — the role of pycuda.pagelocked_empty in
+ *   runtime/worker/llm_worker/kv_worker.py:123-130.
+ * lms_host_alloc returns page-locked, mapped, portable memory in *host_ptr and
+ * its device-visible alias in *device_ptr; lms_host_register pins and maps an
+ * existing allocation.  Free / unregister with the matching call.
+ */
+int lms_host_alloc(int64_t bytes, void** host_ptr, void** device_ptr);
+int lms_host_free(void* host_ptr);
+int lms_host_register(void* host_ptr, int64_t bytes, void** device_ptr);
+int lms_host_unregister(void* host_ptr);
+
+/*
+ * Cross-process mapping of a peer's cache — the role of
+ * UntypedStorage._share_cuda_ / _new_shared_cuda in
+ *   runtime/worker/llm_worker/model_worker.py:284 and kv_worker.py:104-108.
+ * lms_ipc_export fills a 64-byte handle for the allocation that contains
+ * `device_ptr` and the byte offset of device_ptr inside it; lms_ipc_open maps
+ * it in another process and returns base+offset; lms_ipc_close unmaps (pass the
+ * pointer lms_ipc_open returned and the same offset).
+ */
+#define LMS_IPC_HANDLE_BYTES 64
+int lms_ipc_export(void* device_ptr, void* handle64, int64_t* offset);
+int lms_ipc_open(const void* handle64, int64_t offset, void** device_ptr);
+int lms_ipc_close(void* device_ptr, int64_t offset);
+
+/*
+ * Plain cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDefault) on `stream`: the copy-engine
+ * baseline the swap and transfer kernels are measured against (one contiguous DMA).  No
+ * counterpart in the reference, which issues its copies through pycuda
+ * (runtime/worker/llm_worker/kv_worker.py:206-211,222-227).
+ */
+int lms_memcpy_async(void* dst, const void* src, int64_t bytes, void* stream);
+
+/* Number of kernels this library has launched in this process (all threads). */
+int64_t lms_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LMSERVE_KV_H_ */

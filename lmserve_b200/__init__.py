@@ -1,0 +1,15 @@
+"""B200-native KV-cache data movement for LMServe's paged cache.
+
+``lmserve_b200.ops`` mirrors ``llm_worker.ops`` (``copy_blocks``,
+``fill_key_cache`` and the paged/interleaved ``reshape_and_cache``);
+``lmserve_b200.kv_worker`` mirrors the GPU-facing part of ``llm_worker.kv_worker``.
+All device work is done by ``liblmserve_kv.so`` (C ABI: ``include/lmserve_kv.h``).
+"""
+from . import _lib
+from .ops import (copy_blocks, fill_key_cache, reshape_and_cache,
+                  reshape_and_cache_layers, swap_blocks, transfer_blocks)
+
+__version__ = "0.1.0"
+
+__all__ = ["copy_blocks", "fill_key_cache", "reshape_and_cache",
+           "reshape_and_cache_layers", "swap_blocks", "transfer_blocks", "_lib"]

@@ -1,0 +1,444 @@
+// C ABI of the KV-cache data-movement library: argument validation, launch
+// configuration, per-device state (SM count, error record) and the small
+// host-memory / IPC helpers.  Declarations and the reference call sites each
+// entry point replaces are in include/lmserve_kv.h.
+#include <atomic>
+#include <mutex>
+#include <stdio.h>
+#include <string.h>
+
+#include "../../include/lmserve_kv.h"
+#include "kernels.cuh"
+
+namespace {
+
+using namespace lms;
+
+constexpr int kMaxDevices = 64;
+
+struct DeviceState {
+  int sms = 0;
+  ErrRecord* err = nullptr;  // device memory, allocated on first use
+};
+
+std::mutex g_mutex;
+DeviceState g_dev[kMaxDevices];
+std::atomic<int> g_checks{0};
+std::atomic<long long> g_launches{0};
+std::atomic<int> g_tuning[LMS_TUNE__COUNT];
+thread_local char g_cuda_msg[256] = "";
+
+int cuda_fail(cudaError_t e, const char* what) {
+  snprintf(g_cuda_msg, sizeof(g_cuda_msg), "%s: %s (%s)", what,
+           cudaGetErrorName(e), cudaGetErrorString(e));
+  return LMS_ERR_CUDA;
+}
+
+#define LMS_CUDA(call)                                  \
+  do {                                                  \
+    cudaError_t e__ = (call);                           \
+    if (e__ != cudaSuccess) return cuda_fail(e__, #call); \
+  } while (0)
+
+// Per-device state of the current device; allocates the 32-byte error record
+// the first time a device is seen.
+int device_state(DeviceState** out) {
+  int dev = 0;
+  LMS_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return LMS_ERR_RANGE;
+  DeviceState& s = g_dev[dev];
+  if (s.err == nullptr) {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (s.err == nullptr) {
+      LMS_CUDA(cudaDeviceGetAttribute(&s.sms, cudaDevAttrMultiProcessorCount, dev));
+      ErrRecord* e = nullptr;
+      LMS_CUDA(cudaMalloc(&e, sizeof(ErrRecord)));
+      LMS_CUDA(cudaMemset(e, 0, sizeof(ErrRecord)));
+      s.err = e;
+    }
+  }
+  *out = &s;
+  return LMS_OK;
+}
+
+inline bool mult16(long long v) { return (v & 15) == 0; }
+inline bool ptr16(const void* p) { return ((uintptr_t)p & 15u) == 0; }
+
+int tuned(int key, int fallback) {
+  const int v = g_tuning[key].load(std::memory_order_relaxed);
+  return v > 0 ? v : fallback;
+}
+int tuned_variant(int key, int fallback) {
+  // variants are 0..2; stored +1 so that 0 means "not set"
+  const int v = g_tuning[key].load(std::memory_order_relaxed);
+  return v > 0 ? v - 1 : fallback;
+}
+
+int write_layers(const void* key, const void* value, int64_t key_tok,
+                 int64_t val_tok, int64_t key_layer, int64_t val_layer,
+                 void* kcache, void* vcache, int64_t cache_layer,
+                 int64_t block_stride, int64_t slot_stride,
+                 const int64_t* slots, int64_t slot_layer, int64_t num_tokens,
+                 int32_t num_layers, int64_t row_bytes, int32_t block_size,
+                 int64_t num_slots, void* stream) {
+  if (num_tokens < 0 || num_layers < 0 || row_bytes <= 0 || block_size <= 0 ||
+      num_tokens > 0x7fffffffll || row_bytes > (1 << 24) || slot_layer < 0 ||
+      num_slots < 0)
+    return LMS_ERR_RANGE;
+  if (num_tokens == 0 || num_layers == 0) return LMS_OK;
+  if (!key || !value || !kcache || !vcache || !slots) return LMS_ERR_NULL;
+  if (!ptr16(key) || !ptr16(value) || !ptr16(kcache) || !ptr16(vcache) ||
+      ((uintptr_t)slots & 7u) != 0 || !mult16(key_tok) || !mult16(val_tok) ||
+      !mult16(key_layer) || !mult16(val_layer) || !mult16(cache_layer) ||
+      !mult16(block_stride) || !mult16(slot_stride) || !mult16(row_bytes))
+    return LMS_ERR_ALIGN;
+
+  DeviceState* ds = nullptr;
+  if (int rc = device_state(&ds)) return rc;
+
+  WriteParams p{};
+  p.key = (const char*)key;
+  p.value = (const char*)value;
+  p.kcache = (char*)kcache;
+  p.vcache = (char*)vcache;
+  p.slots = (const long long*)slots;
+  p.key_tok = key_tok;
+  p.val_tok = val_tok;
+  p.key_layer = key_layer;
+  p.val_layer = val_layer;
+  p.cache_layer = cache_layer;
+  p.block_stride = block_stride;
+  p.slot_stride = slot_stride;
+  p.slot_layer = slot_layer;
+  p.num_slots = num_slots;
+  p.num_tokens = (int)num_tokens;
+  p.num_layers = num_layers;
+  p.block_size = block_size;
+  p.row_bytes = (int)row_bytes;
+  p.err = ds->err;
+  p.checks = g_checks.load(std::memory_order_relaxed);
+
+  const int variant = tuned_variant(LMS_TUNE_WRITE_VARIANT, 0);
+  const int tile = tuned(LMS_TUNE_WRITE_TILE_BYTES, 0);
+  LMS_CUDA(launch_write(p, variant, tile, (cudaStream_t)stream));
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return LMS_OK;
+}
+
+// Shared validation + launch of the three chunk-copy entry points.
+int chunk_copy(const void* src, int64_t src_layer, int64_t src_block, void* dst,
+               int64_t dst_layer, int64_t dst_block, int64_t chunk_bytes,
+               int32_t num_layers, const int64_t* pairs, int64_t n_pairs,
+               int64_t num_src_blocks, int64_t num_dst_blocks, int layer_major,
+               unsigned where, int variant, int policy, int ctas, void* stream) {
+  if (n_pairs < 0 || num_layers < 0 || chunk_bytes <= 0 ||
+      chunk_bytes > (1ll << 30) || num_src_blocks < 0 || num_dst_blocks < 0)
+    return LMS_ERR_RANGE;
+  if (n_pairs == 0 || num_layers == 0) return LMS_OK;
+  if (!src || !dst || !pairs) return LMS_ERR_NULL;
+  if (!ptr16(src) || !ptr16(dst) || !ptr16(pairs) || !mult16(src_layer) ||
+      !mult16(src_block) || !mult16(dst_layer) || !mult16(dst_block) ||
+      !mult16(chunk_bytes))
+    return LMS_ERR_ALIGN;
+
+  DeviceState* ds = nullptr;
+  if (int rc = device_state(&ds)) return rc;
+
+  CopyParams p{};
+  p.src = (const char*)src;
+  p.dst = (char*)dst;
+  p.src_layer = src_layer;
+  p.src_block = src_block;
+  p.dst_layer = dst_layer;
+  p.dst_block = dst_block;
+  p.pairs = (const long long*)pairs;
+  p.n_pairs = n_pairs;
+  p.num_src_blocks = num_src_blocks;
+  p.num_dst_blocks = num_dst_blocks;
+  p.num_layers = num_layers;
+  p.layer_major = layer_major;
+  p.chunk_bytes = (int)chunk_bytes;
+  p.err = ds->err;
+  p.where = where;
+  p.checks = g_checks.load(std::memory_order_relaxed);
+
+  if (ctas <= 0) ctas = ds->sms * 8;
+  LMS_CUDA(launch_chunk_copy(p, variant, policy, ctas, (cudaStream_t)stream));
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return LMS_OK;
+}
+
+int sm_count() {
+  DeviceState* ds = nullptr;
+  if (device_state(&ds) != LMS_OK) return 148;
+  return ds->sms;
+}
+
+}  // namespace
+
+extern "C" {
+#pragma GCC visibility push(default)
+
+int lms_version(void) { return LMS_VERSION; }
+
+const char* lms_strerror(int status) {
+  switch (status) {
+    case LMS_OK: return "ok";
+    case LMS_ERR_NULL: return "a required pointer is NULL";
+    case LMS_ERR_ALIGN: return "pointer, stride or size is not a multiple of 16 bytes";
+    case LMS_ERR_RANGE: return "argument out of range";
+    case LMS_ERR_CUDA: return "a CUDA call failed (see lms_last_cuda_error)";
+    case LMS_ERR_INDEX: return "a kernel met an out-of-range slot or block index";
+    case LMS_ERR_PEER: return "peer access between the devices is unavailable";
+    case LMS_ERR_UNSUPPORTED: return "unsupported";
+    default: return "unknown status";
+  }
+}
+
+const char* lms_last_cuda_error(void) { return g_cuda_msg; }
+
+int lms_set_tuning(int key, int value) {
+  if (key <= 0 || key >= LMS_TUNE__COUNT) return LMS_ERR_RANGE;
+  const bool is_variant = key == LMS_TUNE_WRITE_VARIANT ||
+                          key == LMS_TUNE_COPY_VARIANT || key == LMS_TUNE_XFER_VARIANT;
+  if (is_variant) {
+    if (value > 2) return LMS_ERR_RANGE;
+    g_tuning[key].store(value < 0 ? 0 : value + 1);
+  } else {
+    g_tuning[key].store(value < 0 ? 0 : value);
+  }
+  return LMS_OK;
+}
+
+int lms_get_tuning(int key) {
+  if (key <= 0 || key >= LMS_TUNE__COUNT) return LMS_ERR_RANGE;
+  const bool is_variant = key == LMS_TUNE_WRITE_VARIANT ||
+                          key == LMS_TUNE_COPY_VARIANT || key == LMS_TUNE_XFER_VARIANT;
+  const int v = g_tuning[key].load();
+  return is_variant ? v - 1 : v;
+}
+
+int lms_set_debug_checks(int enable) {
+  DeviceState* ds = nullptr;
+  if (int rc = device_state(&ds)) return rc;
+  g_checks.store(enable ? 1 : 0);
+  return LMS_OK;
+}
+
+int lms_check_device_errors(void* stream, int64_t* index, int64_t* value) {
+  DeviceState* ds = nullptr;
+  if (int rc = device_state(&ds)) return rc;
+  ErrRecord h{};
+  LMS_CUDA(cudaMemcpyAsync(&h, ds->err, sizeof(h), cudaMemcpyDeviceToHost,
+                           (cudaStream_t)stream));
+  LMS_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+  if (h.code == kErrNone) return LMS_OK;
+  LMS_CUDA(cudaMemsetAsync(ds->err, 0, sizeof(h), (cudaStream_t)stream));
+  LMS_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+  if (index) *index = h.index;
+  if (value) *value = h.value;
+  if (h.code == kErrWaitTimeout) {
+    snprintf(g_cuda_msg, sizeof(g_cuda_msg),
+             "kernel %u gave up waiting for a bulk copy (task %lld)", h.where,
+             h.index);
+    return LMS_ERR_CUDA;
+  }
+  return LMS_ERR_INDEX;
+}
+
+int lms_reshape_and_cache(const void* key, const void* value,
+                          int64_t key_token_stride, int64_t value_token_stride,
+                          void* key_cache, void* value_cache,
+                          int64_t block_stride, int64_t slot_stride,
+                          const int64_t* slot_mapping, int64_t num_tokens,
+                          int64_t row_bytes, int32_t block_size,
+                          int64_t num_slots, void* stream) {
+  return write_layers(key, value, key_token_stride, value_token_stride, 0, 0,
+                      key_cache, value_cache, 0, block_stride, slot_stride,
+                      slot_mapping, 0, num_tokens, 1, row_bytes, block_size,
+                      num_slots, stream);
+}
+
+int lms_reshape_and_cache_layers(const void* key, const void* value,
+                                 int64_t key_token_stride, int64_t value_token_stride,
+                                 int64_t key_layer_stride, int64_t value_layer_stride,
+                                 void* key_cache, void* value_cache,
+                                 int64_t cache_layer_stride,
+                                 int64_t block_stride, int64_t slot_stride,
+                                 const int64_t* slot_mapping, int64_t slot_layer_stride,
+                                 int64_t num_tokens, int32_t num_layers,
+                                 int64_t row_bytes, int32_t block_size,
+                                 int64_t num_slots, void* stream) {
+  return write_layers(key, value, key_token_stride, value_token_stride,
+                      key_layer_stride, value_layer_stride, key_cache,
+                      value_cache, cache_layer_stride, block_stride,
+                      slot_stride, slot_mapping, slot_layer_stride, num_tokens,
+                      num_layers, row_bytes, block_size, num_slots, stream);
+}
+
+int lms_copy_blocks(void* kv, int64_t layer_stride, int64_t block_stride,
+                    int64_t chunk_bytes, int32_t num_layers,
+                    const int64_t* pairs, int64_t n_pairs, int64_t num_blocks,
+                    void* stream) {
+  // Layer-major unit order: CTAs running at the same time work on one layer,
+  // so a source block that fans out to many destinations is re-read from L2.
+  const int per_sm = tuned(LMS_TUNE_COPY_CTAS_PER_SM, 8);
+  return chunk_copy(kv, layer_stride, block_stride, kv, layer_stride,
+                    block_stride, chunk_bytes, num_layers, pairs, n_pairs,
+                    num_blocks, num_blocks, /*layer_major=*/1, kWhereCopyBlocks,
+                    tuned_variant(LMS_TUNE_COPY_VARIANT, 0), /*policy=*/1,
+                    sm_count() * per_sm, stream);
+}
+
+int lms_swap_blocks(int direction, void* gpu, int64_t gpu_layer_stride,
+                    int64_t gpu_block_stride, void* host,
+                    int64_t host_block_stride, int64_t host_layer_stride,
+                    int64_t chunk_bytes, int32_t layer_begin, int32_t layer_end,
+                    const int64_t* pairs, int64_t n_pairs,
+                    int64_t num_gpu_blocks, int64_t num_host_blocks,
+                    void* stream) {
+  if (direction != LMS_SWAP_OUT && direction != LMS_SWAP_IN) return LMS_ERR_RANGE;
+  if (layer_begin < 0 || layer_end < layer_begin) return LMS_ERR_RANGE;
+  if (!gpu || !host) return (n_pairs == 0 || layer_end == layer_begin) ? LMS_OK : LMS_ERR_NULL;
+  const int nl = layer_end - layer_begin;
+  char* g = (char*)gpu + (long long)layer_begin * gpu_layer_stride;
+  char* h = (char*)host + (long long)layer_begin * host_layer_stride;
+  // Pair-major unit order: consecutive units are the layers of one block,
+  // which are adjacent in the block-major host pool.
+  if (direction == LMS_SWAP_OUT)
+    return chunk_copy(g, gpu_layer_stride, gpu_block_stride, h,
+                      host_layer_stride, host_block_stride, chunk_bytes, nl,
+                      pairs, n_pairs, num_gpu_blocks, num_host_blocks,
+                      /*layer_major=*/0, kWhereSwapOut, 0, 0,
+                      tuned(LMS_TUNE_SWAP_OUT_CTAS, sm_count() * 2), stream);
+  return chunk_copy(h, host_layer_stride, host_block_stride, g,
+                    gpu_layer_stride, gpu_block_stride, chunk_bytes, nl, pairs,
+                    n_pairs, num_host_blocks, num_gpu_blocks,
+                    /*layer_major=*/0, kWhereSwapIn, 0, 0,
+                    tuned(LMS_TUNE_SWAP_IN_CTAS, sm_count() * 4), stream);
+}
+
+int lms_transfer_blocks(const void* src, int64_t src_layer_stride,
+                        int64_t src_block_stride, void* dst,
+                        int64_t dst_layer_stride, int64_t dst_block_stride,
+                        int64_t chunk_bytes, int32_t num_layers,
+                        const int64_t* pairs, int64_t n_pairs,
+                        int64_t num_src_blocks, int64_t num_dst_blocks,
+                        void* stream) {
+  const int per_sm = tuned(LMS_TUNE_XFER_CTAS_PER_SM, 4);
+  return chunk_copy(src, src_layer_stride, src_block_stride, dst,
+                    dst_layer_stride, dst_block_stride, chunk_bytes, num_layers,
+                    pairs, n_pairs, num_src_blocks, num_dst_blocks,
+                    /*layer_major=*/1, kWhereTransfer,
+                    tuned_variant(LMS_TUNE_XFER_VARIANT, 0), 0,
+                    sm_count() * per_sm, stream);
+}
+
+int lms_peer_enable(int peer_device) {
+  int dev = 0;
+  LMS_CUDA(cudaGetDevice(&dev));
+  if (peer_device == dev) return LMS_OK;
+  int can = 0;
+  LMS_CUDA(cudaDeviceCanAccessPeer(&can, dev, peer_device));
+  if (!can) return LMS_ERR_PEER;
+  cudaError_t e = cudaDeviceEnablePeerAccess(peer_device, 0);
+  if (e == cudaErrorPeerAccessAlreadyEnabled) {
+    cudaGetLastError();
+    return LMS_OK;
+  }
+  if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceEnablePeerAccess");
+  return LMS_OK;
+}
+
+int lms_host_alloc(int64_t bytes, void** host_ptr, void** device_ptr) {
+  if (!host_ptr || !device_ptr) return LMS_ERR_NULL;
+  if (bytes <= 0) return LMS_ERR_RANGE;
+  void* h = nullptr;
+  LMS_CUDA(cudaHostAlloc(&h, (size_t)bytes, cudaHostAllocMapped | cudaHostAllocPortable));
+  void* d = nullptr;
+  cudaError_t e = cudaHostGetDevicePointer(&d, h, 0);
+  if (e != cudaSuccess) {
+    cudaFreeHost(h);
+    return cuda_fail(e, "cudaHostGetDevicePointer");
+  }
+  *host_ptr = h;
+  *device_ptr = d;
+  return LMS_OK;
+}
+
+int lms_host_free(void* host_ptr) {
+  if (!host_ptr) return LMS_OK;
+  LMS_CUDA(cudaFreeHost(host_ptr));
+  return LMS_OK;
+}
+
+int lms_host_register(void* host_ptr, int64_t bytes, void** device_ptr) {
+  if (!host_ptr || !device_ptr) return LMS_ERR_NULL;
+  if (bytes <= 0) return LMS_ERR_RANGE;
+  LMS_CUDA(cudaHostRegister(host_ptr, (size_t)bytes,
+                            cudaHostRegisterMapped | cudaHostRegisterPortable));
+  void* d = nullptr;
+  cudaError_t e = cudaHostGetDevicePointer(&d, host_ptr, 0);
+  if (e != cudaSuccess) {
+    cudaHostUnregister(host_ptr);
+    return cuda_fail(e, "cudaHostGetDevicePointer");
+  }
+  *device_ptr = d;
+  return LMS_OK;
+}
+
+int lms_host_unregister(void* host_ptr) {
+  if (!host_ptr) return LMS_OK;
+  LMS_CUDA(cudaHostUnregister(host_ptr));
+  return LMS_OK;
+}
+
+int lms_ipc_export(void* device_ptr, void* handle64, int64_t* offset) {
+  if (!device_ptr || !handle64 || !offset) return LMS_ERR_NULL;
+  static_assert(sizeof(cudaIpcMemHandle_t) == LMS_IPC_HANDLE_BYTES, "handle size");
+  // The handle names the whole allocation; find its base through the driver.
+  typedef int (*GetRangeFn)(unsigned long long*, size_t*, unsigned long long);
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult qr;
+  LMS_CUDA(cudaGetDriverEntryPoint("cuMemGetAddressRange", &fn, cudaEnableDefault, &qr));
+  if (!fn || qr != cudaDriverEntryPointSuccess) return LMS_ERR_UNSUPPORTED;
+  unsigned long long base = 0;
+  size_t size = 0;
+  if (((GetRangeFn)fn)(&base, &size, (unsigned long long)(uintptr_t)device_ptr) != 0)
+    return LMS_ERR_RANGE;
+  cudaIpcMemHandle_t h;
+  LMS_CUDA(cudaIpcGetMemHandle(&h, (void*)(uintptr_t)base));
+  memcpy(handle64, &h, sizeof(h));
+  *offset = (int64_t)((unsigned long long)(uintptr_t)device_ptr - base);
+  return LMS_OK;
+}
+
+int lms_ipc_open(const void* handle64, int64_t offset, void** device_ptr) {
+  if (!handle64 || !device_ptr) return LMS_ERR_NULL;
+  if (offset < 0) return LMS_ERR_RANGE;
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, sizeof(h));
+  void* base = nullptr;
+  LMS_CUDA(cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess));
+  *device_ptr = (char*)base + offset;
+  return LMS_OK;
+}
+
+int lms_ipc_close(void* device_ptr, int64_t offset) {
+  if (!device_ptr) return LMS_OK;
+  LMS_CUDA(cudaIpcCloseMemHandle((char*)device_ptr - offset));
+  return LMS_OK;
+}
+
+int lms_memcpy_async(void* dst, const void* src, int64_t bytes, void* stream) {
+  if (!dst || !src) return bytes == 0 ? LMS_OK : LMS_ERR_NULL;
+  if (bytes < 0) return LMS_ERR_RANGE;
+  if (bytes == 0) return LMS_OK;
+  LMS_CUDA(cudaMemcpyAsync(dst, src, (size_t)bytes, cudaMemcpyDefault, (cudaStream_t)stream));
+  return LMS_OK;
+}
+
+int64_t lms_launch_count(void) { return g_launches.load(); }
+
+#pragma GCC visibility pop
+}  // extern "C"

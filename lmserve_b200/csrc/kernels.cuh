@@ -1,0 +1,80 @@
+// Parameter blocks and host-side launchers of the data-movement kernels.
+// The C ABI (capi.cu) validates arguments, fills these structs and calls the
+// launchers; the kernels themselves live in write_rows.cu and chunk_copy.cu.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "kv_common.cuh"
+
+namespace lms {
+
+// Kernel ids written into ErrRecord::where.
+enum : unsigned int {
+  kWhereWrite = 1,
+  kWhereCopyBlocks = 2,
+  kWhereSwapOut = 3,
+  kWhereSwapIn = 4,
+  kWhereTransfer = 5,
+};
+
+// ------------------------------------------------------------ paged cache write
+struct WriteParams {
+  const char* key;
+  const char* value;
+  char* kcache;
+  char* vcache;
+  const long long* slots;
+  long long key_tok, val_tok;      // bytes between consecutive tokens
+  long long key_layer, val_layer;  // bytes between consecutive layers (inputs)
+  long long cache_layer;           // bytes between consecutive layers (cache)
+  long long block_stride;          // bytes between consecutive cache blocks
+  long long slot_stride;           // bytes between consecutive slots in a block
+  long long slot_layer;            // elements between per-layer slot tables (0 = shared)
+  long long num_slots;             // bound for the debug checks (0 = unchecked)
+  int num_tokens;
+  int num_layers;
+  int block_size;
+  int block_shift;      // log2(block_size) or -1
+  int row_bytes;
+  int tok_tile;         // tokens per CTA (vector kernels)
+  int tiles_per_layer;
+  int piece_bytes;      // bulk kernel: bytes moved per lane
+  int pieces_per_row;
+  ErrRecord* err;
+  int checks;
+};
+
+// variant: 0 = 16-byte vectors, 1 = 32-byte vectors, 2 = bulk copies
+cudaError_t launch_write(const WriteParams& p, int variant, int tile_bytes,
+                         cudaStream_t stream);
+
+// ------------------------------------------------------------ chunk copies
+// One kernel family serves copy_blocks, swap-out, swap-in and transfer: every
+// unit of work copies (a slice of) the chunk of one (layer, pair).
+struct CopyParams {
+  const char* src;
+  char* dst;
+  long long src_layer, src_block;  // byte strides on the source side
+  long long dst_layer, dst_block;  // byte strides on the destination side
+  const long long* pairs;          // [n_pairs][2] = (src block, dst block)
+  long long n_pairs;
+  long long num_src_blocks, num_dst_blocks;  // debug-check bounds (0 = unchecked)
+  long long units;                 // num_layers * n_pairs * slices
+  int num_layers;
+  int layer_major;   // 1: consecutive units walk pairs of one layer; 0: layers of one pair
+  int chunk_bytes;
+  int slice_bytes;   // bytes one CTA iteration (vector) / one lane (bulk) moves
+  int slices;        // slices per chunk
+  ErrRecord* err;
+  unsigned int where;
+  int checks;
+};
+
+// variant as above; policy: 0 = default caching, 1 = sources kept in L2 and
+// destinations streamed (fan-out copies).
+cudaError_t launch_chunk_copy(const CopyParams& p, int variant, int policy,
+                              int grid_ctas, cudaStream_t stream);
+
+}  // namespace lms

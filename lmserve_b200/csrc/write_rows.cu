@@ -1,0 +1,253 @@
+// Paged KV-cache write ("reshape_and_cache") for sm_100a.
+//
+// Work: for every (layer, token, K|V) copy one row of row_bytes from the
+// projection output into the paged cache at the address the token's slot
+// selects; slot < 0 is padding and is skipped.  Pure byte movement, bound by
+// HBM bandwidth: 2 * row_bytes read and 2 * row_bytes written per live token
+// per layer.
+//
+// Two implementations share one parameter block:
+//   * write_rows_vec  - a CTA owns a tile of tokens of one layer.  Slots are
+//     turned into destination byte offsets once, in shared memory; then every
+//     thread moves VPT 16- or 32-byte vectors with all loads issued before the
+//     first store, so a CTA keeps THREADS*VPT vectors in flight.
+//   * write_rows_bulk - every lane of a warp owns one piece of a row and moves
+//     it with a bulk (TMA) copy global -> shared -> global; the warp shares one
+//     mbarrier.  Almost no instructions per byte.
+#include "kernels.cuh"
+
+namespace lms {
+
+namespace {
+
+constexpr int kMaxTokTile = 512;
+
+// slot -> byte offset of the row inside one layer's K (or V) plane, or -1.
+__device__ __forceinline__ long long slot_offset(const WriteParams& p,
+                                                 long long slot, long long index) {
+  if (slot < 0) return -1;
+  if (p.checks && p.num_slots > 0 && slot >= p.num_slots) {
+    report(p.err, kErrBadSlot, kWhereWrite, index, slot);
+    return -1;
+  }
+  long long blk, in;
+  if (p.block_shift >= 0) {
+    blk = slot >> p.block_shift;
+    in = slot & ((1ll << p.block_shift) - 1);
+  } else {
+    blk = slot / p.block_size;
+    in = slot - blk * p.block_size;
+  }
+  return blk * p.block_stride + in * p.slot_stride;
+}
+
+template <class Vec, int THREADS, int VPT, bool POW2>
+__global__ void __launch_bounds__(THREADS)
+write_rows_vec(const WriteParams p, const int row_vecs, const int row_shift) {
+  __shared__ long long s_off[kMaxTokTile];
+
+  const int tile = blockIdx.x % p.tiles_per_layer;
+  const int layer = blockIdx.x / p.tiles_per_layer;
+  const int t0 = tile * p.tok_tile;
+  const int nt = min(p.tok_tile, p.num_tokens - t0);
+
+  const long long* slots = p.slots + (long long)layer * p.slot_layer + t0;
+  for (int i = threadIdx.x; i < nt; i += THREADS)
+    s_off[i] = slot_offset(p, slots[i], (long long)layer * p.slot_layer + t0 + i);
+  __syncthreads();
+
+  const char* kin = p.key + (long long)layer * p.key_layer + (long long)t0 * p.key_tok;
+  const char* vin = p.value + (long long)layer * p.val_layer + (long long)t0 * p.val_tok;
+  char* kout = p.kcache + (long long)layer * p.cache_layer;
+  char* vout = p.vcache + (long long)layer * p.cache_layer;
+
+  const int vecs_per_tok = 2 * row_vecs;
+  const int n_vec = nt * vecs_per_tok;
+
+  for (int base = 0; base < n_vec; base += THREADS * VPT) {
+    Vec r[VPT];
+    char* d[VPT];
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      const int v = base + k * THREADS + threadIdx.x;
+      d[k] = nullptr;
+      if (v < n_vec) {
+        int ti, kv, c;
+        if (POW2) {
+          ti = v >> (row_shift + 1);
+          kv = (v >> row_shift) & 1;
+          c = v & (row_vecs - 1);
+        } else {
+          ti = v / vecs_per_tok;
+          const int rem = v - ti * vecs_per_tok;
+          kv = rem >= row_vecs;
+          c = rem - kv * row_vecs;
+        }
+        const long long off = s_off[ti];
+        if (off >= 0) {
+          const char* s = kv ? vin + (long long)ti * p.val_tok
+                             : kin + (long long)ti * p.key_tok;
+          ld(r[k], s + (long long)c * Vec::kBytes);
+          d[k] = (kv ? vout : kout) + off + (long long)c * Vec::kBytes;
+        }
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < VPT; ++k)
+      if (d[k] != nullptr) st(d[k], r[k]);
+  }
+}
+
+// One piece per lane per iteration; a warp-task is 32 consecutive pieces of
+// the flattened (layer, token, K|V, piece) index space.
+template <int WARPS>
+__global__ void __launch_bounds__(WARPS * 32)
+write_rows_bulk(const WriteParams p, const long long n_items) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ uint64_t bars[WARPS];
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  uint64_t* bar = &bars[warp];
+  unsigned char* buf = smem + ((size_t)warp * 32 + lane) * p.piece_bytes;
+
+  if (lane == 0) {
+    mbar_init(bar, 1);
+    mbar_fence_init();
+  }
+  __syncwarp();
+
+  const long long n_tasks = (n_items + 31) / 32;
+  const long long warp_stride = (long long)gridDim.x * WARPS;
+  unsigned parity = 0;
+
+  for (long long task = (long long)blockIdx.x * WARPS + warp;
+       task < n_tasks; task += warp_stride) {
+    const long long item = task * 32 + lane;
+    const char* src = nullptr;
+    char* dst = nullptr;
+    if (item < n_items) {
+      // item = ((layer * T + t) * 2 + kv) * pieces_per_row + piece
+      const int piece = (int)(item % p.pieces_per_row);
+      long long q = item / p.pieces_per_row;
+      const int kv = (int)(q & 1);
+      q >>= 1;
+      const int t = (int)(q % p.num_tokens);
+      const int layer = (int)(q / p.num_tokens);
+      const long long si = (long long)layer * p.slot_layer + t;
+      const long long off = slot_offset(p, p.slots[si], si);
+      if (off >= 0) {
+        const long long po = (long long)piece * p.piece_bytes;
+        src = (kv ? p.value + (long long)layer * p.val_layer + (long long)t * p.val_tok
+                  : p.key + (long long)layer * p.key_layer + (long long)t * p.key_tok) + po;
+        dst = (kv ? p.vcache : p.kcache) + (long long)layer * p.cache_layer + off + po;
+      }
+    }
+    const unsigned live = __ballot_sync(0xffffffffu, src != nullptr);
+    if (live == 0) continue;
+    if (lane == 0) mbar_expect_tx(bar, (unsigned)__popc(live) * (unsigned)p.piece_bytes);
+    __syncwarp();
+    if (src != nullptr) bulk_g2s(buf, src, (unsigned)p.piece_bytes, bar);
+    const unsigned phase = parity;
+    parity ^= 1u;
+    const bool ok = mbar_wait_bounded(bar, phase);
+    if (__any_sync(0xffffffffu, !ok)) {
+      // The loads never landed: say so, store nothing, stop taking work.  One
+      // more short bounded wait lets copies still in flight land before this
+      // CTA's shared memory is released.
+      if (lane == 0) report(p.err, kErrWaitTimeout, kWhereWrite, task, 0);
+      mbar_wait_bounded(bar, phase, 100000000ull);
+      break;
+    }
+    if (src != nullptr) {
+      bulk_s2g(dst, buf, (unsigned)p.piece_bytes);
+      bulk_commit();
+      bulk_wait_read_all();
+    }
+    __syncwarp();
+  }
+  bulk_wait_all();
+}
+
+inline int ilog2_exact(long long x) {
+  if (x <= 0 || (x & (x - 1)) != 0) return -1;
+  int s = 0;
+  while ((1ll << s) < x) ++s;
+  return s;
+}
+
+template <class Vec>
+cudaError_t launch_vec(WriteParams p, int tile_bytes, cudaStream_t stream) {
+  constexpr int THREADS = 256;
+  constexpr int VPT = 8;
+  const int row_vecs = p.row_bytes / Vec::kBytes;
+  const int row_shift = ilog2_exact(row_vecs);
+  if (tile_bytes <= 0) tile_bytes = THREADS * VPT * Vec::kBytes;
+  int tok_tile = tile_bytes / (2 * p.row_bytes);
+  tok_tile = tok_tile < 1 ? 1 : (tok_tile > kMaxTokTile ? kMaxTokTile : tok_tile);
+  if (tok_tile > p.num_tokens) tok_tile = p.num_tokens;
+  p.tok_tile = tok_tile;
+  p.tiles_per_layer = (p.num_tokens + tok_tile - 1) / tok_tile;
+  const long long ctas = (long long)p.tiles_per_layer * p.num_layers;
+  if (ctas > 0x7fffffffll) return cudaErrorInvalidConfiguration;
+  if (row_shift >= 0)
+    write_rows_vec<Vec, THREADS, VPT, true>
+        <<<(unsigned)ctas, THREADS, 0, stream>>>(p, row_vecs, row_shift);
+  else
+    write_rows_vec<Vec, THREADS, VPT, false>
+        <<<(unsigned)ctas, THREADS, 0, stream>>>(p, row_vecs, row_shift);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_write(const WriteParams& p_in, int variant, int tile_bytes,
+                         cudaStream_t stream) {
+  WriteParams p = p_in;
+  p.block_shift = ilog2_exact(p.block_size);
+
+  // 32-byte vectors need 32-byte alignment of every address they touch.
+  auto aligned32 = [&]() {
+    const uintptr_t ptrs = (uintptr_t)p.key | (uintptr_t)p.value |
+                           (uintptr_t)p.kcache | (uintptr_t)p.vcache;
+    const long long strides = p.key_tok | p.val_tok | p.key_layer | p.val_layer |
+                              p.cache_layer | p.block_stride | p.slot_stride |
+                              (long long)p.row_bytes;
+    return ((ptrs | (uintptr_t)strides) & 31u) == 0;
+  };
+  if (variant == 1 && !aligned32()) variant = 0;
+
+  if (variant == 2) {
+    // piece = the largest power-of-two divisor of the row, capped at 1 KiB
+    int piece = 1024;
+    while (piece > 16 && (p.row_bytes % piece) != 0) piece >>= 1;
+    p.piece_bytes = piece;
+    p.pieces_per_row = p.row_bytes / piece;
+    const long long n_items =
+        (long long)p.num_layers * p.num_tokens * 2 * p.pieces_per_row;
+    constexpr int WARPS = 2;
+    const size_t smem = (size_t)WARPS * 32 * piece;
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    static bool attr_set[64] = {};
+    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+      cudaError_t e = cudaFuncSetAttribute(write_rows_bulk<WARPS>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           WARPS * 32 * 1024);
+      if (e != cudaSuccess) return e;
+      if (dev >= 0 && dev < 64) attr_set[dev] = true;
+    }
+    const long long tasks = (n_items + 31) / 32;
+    long long ctas = (tasks + WARPS - 1) / WARPS;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const long long resident = (long long)sms * ((200 * 1024) / (long long)(smem + 1024));
+    if (ctas > resident) ctas = resident;
+    if (ctas < 1) ctas = 1;
+    write_rows_bulk<WARPS><<<(unsigned)ctas, WARPS * 32, smem, stream>>>(p, n_items);
+    return cudaGetLastError();
+  }
+  if (variant == 1) return launch_vec<V32>(p, tile_bytes, stream);
+  return launch_vec<V16>(p, tile_bytes, stream);
+}
+
+}  // namespace lms

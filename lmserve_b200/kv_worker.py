@@ -1,0 +1,291 @@
+"""Host-side mirror of LMServe's ``KVWorker`` (``runtime/worker/llm_worker/kv_worker.py``)
+for the parts that move KV blocks through the GPU: the pinned host pool, the
+GPU<->host swap in both directions with the per-layer event handshake, and the
+prefill->decode push — here a direct GPU->GPU store over NVLink instead of the
+reference's NIXL/UCX host-to-host write.
+
+Not mirrored (no GPU data path): the disk tier (``kv_worker.py:229-247,297-322``)
+and the NIXL agent bookkeeping.
+"""
+from __future__ import annotations
+
+import ctypes
+import enum
+import pickle
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from . import _lib
+from .ops import cache_ops
+
+
+class Device(enum.IntEnum):
+    """``Device`` of ``proto/worker.proto:13-17``."""
+    GPU = 0
+    Host = 1
+    Disk = 2
+
+
+@dataclass
+class BlockMappingEntry:
+    """``BlockMappingEntry`` of ``proto/worker.proto:78-81``."""
+    src_block_id: int
+    dst_block_id: int
+
+
+@dataclass
+class BlockMapping:
+    """``BlockMapping`` of ``proto/worker.proto:83-86``: a list of (src, dst) block ids."""
+    entries: List[BlockMappingEntry] = field(default_factory=list)
+
+    @classmethod
+    def from_pairs(cls, pairs) -> "BlockMapping":
+        return cls([BlockMappingEntry(int(s), int(d)) for s, d in pairs])
+
+
+def mappings_to_pairs(block_mappings: Sequence) -> np.ndarray:
+    """Concatenates the entries of several BlockMappings into one int64 [n, 2] table.
+
+    Accepts the dataclasses above, protobuf messages with the same field names,
+    or ready-made [n, 2] arrays.
+    """
+    chunks = []
+    for m in block_mappings:
+        if isinstance(m, (np.ndarray, torch.Tensor)):
+            chunks.append(cache_ops.flatten_block_map(m))
+            continue
+        entries = m.entries
+        arr = np.empty((len(entries), 2), dtype=np.int64)
+        for i, e in enumerate(entries):
+            arr[i, 0] = e.src_block_id
+            arr[i, 1] = e.dst_block_id
+        chunks.append(arr)
+    if not chunks:
+        return np.empty((0, 2), dtype=np.int64)
+    return np.concatenate(chunks, axis=0)
+
+
+class HostPool:
+    """Page-locked, GPU-mapped host KV pool ``[num_blocks, num_layers, chunk_bytes]``.
+
+    The block-major layout and the pinning follow ``kv_worker.py:123-130``
+    (``pycuda.pagelocked_empty((num_host_blocks, num_layers, block_size), ...)``);
+    the pool is additionally *mapped*, so the swap kernels address it directly.
+    bf16 payloads are held as raw bytes, as the reference holds them as uint16.
+    """
+
+    def __init__(self, num_blocks: int, num_layers: int, chunk_bytes: int):
+        if num_blocks <= 0 or num_layers <= 0 or chunk_bytes <= 0 or chunk_bytes % 16:
+            raise ValueError("host pool needs positive sizes and a chunk that is a multiple of 16 bytes")
+        self.num_blocks = int(num_blocks)
+        self.num_layers = int(num_layers)
+        self.chunk_bytes = int(chunk_bytes)
+        self.layer_stride = self.chunk_bytes
+        self.block_stride = self.num_layers * self.chunk_bytes
+        self.nbytes = self.num_blocks * self.block_stride
+        hp, dp = ctypes.c_void_p(), ctypes.c_void_p()
+        _lib.check(_lib.lib().lms_host_alloc(self.nbytes, ctypes.byref(hp), ctypes.byref(dp)))
+        self.host_ptr = hp.value
+        self.device_ptr = dp.value
+        buf = (ctypes.c_uint8 * self.nbytes).from_address(self.host_ptr)
+        self.array = np.frombuffer(buf, dtype=np.uint8).reshape(
+            self.num_blocks, self.num_layers, self.chunk_bytes)
+        self.tensor = torch.from_numpy(self.array)
+
+    def close(self) -> None:
+        if getattr(self, "host_ptr", None):
+            self.tensor = None
+            self.array = None
+            _lib.check(_lib.lib().lms_host_free(self.host_ptr))
+            self.host_ptr = None
+            self.device_ptr = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+@dataclass
+class CacheDescriptor:
+    """What a decode-side worker hands to a prefill-side worker so it can push blocks:
+    the GPU-direct counterpart of the serialized NIXL descriptors of
+    ``kv_worker.py:348-356`` (one descriptor per reserved block there; one IPC
+    handle for the whole cache plus the reserved block ids here)."""
+    handle: bytes
+    offset: int
+    device_index: int
+    num_layers: int
+    num_blocks: int
+    layer_stride: int
+    block_stride: int
+    chunk_bytes: int
+    block_ids: List[int]
+
+    def serialize(self) -> bytes:
+        return pickle.dumps(self.__dict__)
+
+    @classmethod
+    def deserialize(cls, data: bytes) -> "CacheDescriptor":
+        return cls(**pickle.loads(data))
+
+
+class PeerCache:
+    """Another process's GPU cache mapped into this process (``lms_ipc_open``)."""
+
+    def __init__(self, desc: CacheDescriptor):
+        self.desc = desc
+        self.num_layers = desc.num_layers
+        self.num_blocks = desc.num_blocks
+        self.layer_stride = desc.layer_stride
+        self.block_stride = desc.block_stride
+        self.chunk_bytes = desc.chunk_bytes
+        buf = ctypes.create_string_buffer(desc.handle, _lib_handle_bytes())
+        out = ctypes.c_void_p()
+        _lib.check(_lib.lib().lms_ipc_open(buf, desc.offset, ctypes.byref(out)))
+        self.device_ptr = out.value
+
+    def close(self) -> None:
+        if getattr(self, "device_ptr", None):
+            _lib.check(_lib.lib().lms_ipc_close(self.device_ptr, self.desc.offset))
+            self.device_ptr = None
+
+
+def _lib_handle_bytes() -> int:
+    return 64
+
+
+class KVWorker:
+    """Per-GPU mover of KV blocks, API-compatible with the GPU-facing part of LMServe's
+    ``KVWorker`` (``kv_worker.py:88-195,249-295,336-415``).
+
+    ``gpu_kv_caches`` is the model's ``[L, num_gpu_blocks, 2, block_size, H, D]``
+    tensor (or its ``[L, num_gpu_blocks, chunk]`` view); the worker does not own it.
+    """
+
+    def __init__(self, name: str, gpu_kv_caches: torch.Tensor, num_host_blocks: int = 0):
+        cache_ops._require_cuda("gpu_kv_caches", gpu_kv_caches)
+        self.name = name
+        self.gpu_kv_caches = gpu_kv_caches
+        self.device = gpu_kv_caches.device
+        (self.num_layers, self.num_gpu_blocks, self.layer_stride,
+         self.block_stride, self.chunk_bytes) = cache_ops._cache_geometry(gpu_kv_caches)
+        self.host_pool = (HostPool(num_host_blocks, self.num_layers, self.chunk_bytes)
+                          if num_host_blocks > 0 else None)
+        with torch.cuda.device(self.device):
+            self.dtoh_stream = torch.cuda.Stream()
+            self.htod_stream = torch.cuda.Stream()
+            self.push_stream = torch.cuda.Stream()
+        self._peers: Dict[str, PeerCache] = {}
+        self.COPY_KV_OP_MAP = {
+            (Device.GPU, Device.Host): self.save_kv_blocks_to_host,
+            (Device.Host, Device.GPU): self.load_kv_blocks_from_host,
+        }
+
+    # -- swap -----------------------------------------------------------------
+    def load_kv_blocks_from_host(self, block_mappings, stream: Optional[torch.cuda.Stream] = None,
+                                 pre_events: Optional[Sequence[torch.cuda.Event]] = None,
+                                 layers_per_launch: Optional[int] = None) -> None:
+        """Host -> GPU fetch (``kv_worker.py:249-270``).
+
+        With ``pre_events`` the fetch runs ``layers_per_launch`` layers at a time
+        (default 1, like the reference) and records ``pre_events[l]`` on the copy
+        stream once layer ``l`` has landed, so the forward pass can wait per layer;
+        without them it is one launch over all layers.
+        """
+        self._swap(block_mappings, "in", stream or self.htod_stream, pre_events, None,
+                   layers_per_launch)
+
+    def save_kv_blocks_to_host(self, block_mappings, stream: Optional[torch.cuda.Stream] = None,
+                               post_events: Optional[Sequence[torch.cuda.Event]] = None,
+                               layers_per_launch: Optional[int] = None) -> None:
+        """GPU -> host write-through (``kv_worker.py:272-295``).
+
+        With ``post_events`` the copy stream waits for ``post_events[l]`` (recorded by
+        the model after layer ``l``'s attention) before layer ``l`` is copied.
+        """
+        self._swap(block_mappings, "out", stream or self.dtoh_stream, None, post_events,
+                   layers_per_launch)
+
+    def _swap(self, block_mappings, direction, stream, pre_events, post_events, group) -> None:
+        if self.host_pool is None:
+            raise RuntimeError("this KVWorker was created without a host pool")
+        pairs_np = mappings_to_pairs(block_mappings)
+        if pairs_np.shape[0] == 0:
+            return
+        events = pre_events if pre_events is not None else post_events
+        L = self.num_layers
+        with torch.cuda.device(self.device), torch.cuda.stream(stream):
+            pairs = cache_ops._pairs_on_device(pairs_np, self.device)
+            if events is None:
+                cache_ops.swap_blocks(self.gpu_kv_caches, self.host_pool, pairs, direction)
+                return
+            step = max(1, int(group or 1))
+            for l0 in range(0, L, step):
+                l1 = min(L, l0 + step)
+                if post_events is not None:
+                    for l in range(l0, l1):
+                        stream.wait_event(post_events[l])
+                cache_ops.swap_blocks(self.gpu_kv_caches, self.host_pool, pairs, direction,
+                                      layers=(l0, l1))
+                if pre_events is not None:
+                    for l in range(l0, l1):
+                        pre_events[l].record(stream)
+
+    def copy_kv(self, block_mappings, src: Device, dst: Device, **kw) -> None:
+        """``KVWorker.copy_kv`` (``kv_worker.py:336-346``): dispatch on (src, dst)."""
+        key = (src, dst)
+        if key not in self.COPY_KV_OP_MAP:
+            raise ValueError(f"Unsupported copy direction: {src} -> {dst}")
+        self.COPY_KV_OP_MAP[key](block_mappings, **kw)
+
+    # -- prefill -> decode ----------------------------------------------------
+    def get_descriptors(self, block_ids: Sequence[int]) -> bytes:
+        """Serialized descriptor of this worker's GPU cache and the reserved blocks
+        (role of ``kv_worker.py:348-356``)."""
+        handle = ctypes.create_string_buffer(_lib_handle_bytes())
+        offset = ctypes.c_int64()
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.lib().lms_ipc_export(self.gpu_kv_caches.data_ptr(), handle,
+                                                 ctypes.byref(offset)))
+        return CacheDescriptor(handle.raw, offset.value, self.device.index, self.num_layers,
+                               self.num_gpu_blocks, self.layer_stride, self.block_stride,
+                               self.chunk_bytes, [int(b) for b in block_ids]).serialize()
+
+    def push_kv(self, peer_name: str, remote_descs: bytes, block_ids: Sequence[int],
+                stream: Optional[torch.cuda.Stream] = None) -> bool:
+        """Pushes local GPU blocks ``block_ids`` into the peer's reserved blocks
+        (role of ``kv_worker.py:358-415``).  As there, surplus remote blocks are
+        dropped so that both lists have ``len(block_ids)`` entries.  Returns False
+        (after printing the reason) instead of raising, like the reference."""
+        try:
+            desc = CacheDescriptor.deserialize(remote_descs)
+            remote_ids = desc.block_ids[:len(block_ids)]
+            if len(remote_ids) != len(block_ids):
+                print("Creating transfer failed.")
+                return False
+            with torch.cuda.device(self.device):
+                peer = self._peers.get(peer_name)
+                if peer is None:
+                    peer = PeerCache(desc)
+                    self._peers[peer_name] = peer
+                pairs = np.stack([np.asarray(block_ids, dtype=np.int64),
+                                  np.asarray(remote_ids, dtype=np.int64)], axis=1)
+                with torch.cuda.stream(stream or self.push_stream):
+                    cache_ops.transfer_blocks(self.gpu_kv_caches, peer, pairs)
+            return True
+        except _lib.LmsError as e:
+            print(f"Posting transfer failed. {e}")
+            return False
+
+    def close(self) -> None:
+        for p in self._peers.values():
+            p.close()
+        self._peers.clear()
+        if self.host_pool is not None:
+            self.host_pool.close()
+            self.host_pool = None

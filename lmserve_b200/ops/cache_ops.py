@@ -1,0 +1,334 @@
+"""Paged KV-cache operators with LMServe's Python signatures, backed by the
+sm_100a kernels behind the C ABI (``include/lmserve_kv.h``).
+
+``copy_blocks`` and ``fill_key_cache`` keep the names, argument order and
+in-place semantics of ``runtime/worker/llm_worker/ops/cache_ops.py:8-59`` in
+LMServe.  ``reshape_and_cache`` is the same write addressed into the
+interleaved per-layer cache ``[num_blocks, 2, block_size, H, D]`` that
+``models/layers/attention.py:76-85`` fills through flashinfer;
+``reshape_and_cache_layers`` does all layers in one launch.  ``swap_blocks`` and
+``transfer_blocks`` carry the device work of ``kv_worker.py:197-227`` and
+``kv_worker.py:358-415``.
+
+Every operator runs on the current CUDA stream of the cache tensor's device and
+returns without synchronising.  There is no CPU path: tensors that are not on a
+CUDA device are rejected, and a missing shared library is an ImportError.
+"""
+from __future__ import annotations
+
+from typing import Dict, Iterable, List, Optional, Sequence, Tuple, Union
+
+import numpy as np
+import torch
+
+from .. import _lib
+
+PairList = Union[Sequence[Tuple[int, int]], np.ndarray, torch.Tensor]
+
+
+def _stream_ptr(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _require_cuda(name: str, t: torch.Tensor) -> None:
+    if not isinstance(t, torch.Tensor):
+        raise TypeError(f"{name} must be a torch.Tensor, got {type(t).__name__}")
+    if not t.is_cuda:
+        raise RuntimeError(
+            f"{name} must live on a CUDA device (got {t.device}); the cache ops have no CPU path")
+
+
+def _row_layout(name: str, t: torch.Tensor) -> Tuple[int, int]:
+    """(token stride in bytes, row bytes) of a [T, H, D] tensor whose rows are dense."""
+    if t.dim() != 3:
+        raise ValueError(f"{name} must be [num_tokens, num_kv_heads, head_dim], got {tuple(t.shape)}")
+    T, H, D = t.shape
+    es = t.element_size()
+    if T > 0 and (t.stride(2) != 1 or (H > 1 and t.stride(1) != D)):
+        raise ValueError(f"{name}: each token's [H, D] row must be contiguous (strides {t.stride()})")
+    return t.stride(0) * es, H * D * es
+
+
+def _slots_i64(slot_mapping: torch.Tensor, device: torch.device) -> torch.Tensor:
+    if slot_mapping.dtype in (torch.float16, torch.bfloat16, torch.float32, torch.float64, torch.bool):
+        raise TypeError(f"slot_mapping must be an integer tensor, got {slot_mapping.dtype}")
+    if slot_mapping.device != device or slot_mapping.dtype != torch.int64:
+        slot_mapping = slot_mapping.to(device=device, dtype=torch.int64, non_blocking=True)
+    return slot_mapping.contiguous()
+
+
+def flatten_block_map(src_to_dst: Union[Dict[int, Iterable[int]], PairList]) -> np.ndarray:
+    """``{src: [dst, ...]}`` or a sequence of ``(src, dst)`` -> int64 array [n, 2].
+
+    The dict form is what ``copy_blocks`` receives in LMServe
+    (``cache_ops.py:12-15``); the pair form is the shape of
+    ``BlockMapping.entries`` (``proto/worker.proto:78-86``).
+    """
+    if isinstance(src_to_dst, dict):
+        n = sum(len(v) for v in src_to_dst.values())
+        out = np.empty((n, 2), dtype=np.int64)
+        i = 0
+        for src, dsts in src_to_dst.items():
+            k = len(dsts)
+            out[i:i + k, 0] = src
+            out[i:i + k, 1] = np.asarray(dsts, dtype=np.int64) if k else 0
+            i += k
+        return out
+    if isinstance(src_to_dst, torch.Tensor):
+        arr = src_to_dst.detach().cpu().numpy()
+    else:
+        arr = np.asarray(src_to_dst)
+    if arr.size == 0:
+        return np.empty((0, 2), dtype=np.int64)
+    if arr.ndim != 2 or arr.shape[1] != 2:
+        raise ValueError(f"block pairs must have shape [n, 2], got {arr.shape}")
+    if not np.issubdtype(arr.dtype, np.integer):
+        raise TypeError(f"block ids must be integers, got {arr.dtype}")
+    return np.ascontiguousarray(arr, dtype=np.int64)
+
+
+def _pairs_on_device(pairs, device: torch.device) -> torch.Tensor:
+    """int64 [n, 2] on `device`; host tables go through pinned memory, asynchronously."""
+    if isinstance(pairs, torch.Tensor) and pairs.is_cuda:
+        if pairs.dim() != 2 or pairs.shape[1] != 2:
+            raise ValueError(f"block pairs must have shape [n, 2], got {tuple(pairs.shape)}")
+        return pairs.to(device=device, dtype=torch.int64).contiguous()
+    arr = flatten_block_map(pairs)
+    if arr.shape[0] == 0:
+        return torch.empty((0, 2), dtype=torch.int64, device=device)
+    host = torch.from_numpy(arr).pin_memory()
+    return host.to(device, non_blocking=True)
+
+
+# --------------------------------------------------------------------- writes
+def fill_key_cache(
+    key: torch.Tensor,
+    value: torch.Tensor,
+    key_cache: torch.Tensor,
+    value_cache: torch.Tensor,
+    slot_mapping: torch.Tensor,
+) -> None:
+    """``key_cache[slot_mapping[t]] = key[t]`` and the same for value, in place.
+
+    Same contract as LMServe's ``fill_key_cache`` (``ops/cache_ops.py:39-59``,
+    kernel ``ops/triton/cache_kernels.py:39-58``): ``key``/``value`` are
+    ``[T, H, D]``, the two caches are contiguous and addressed as
+    ``[num_slots, H, D]``.  One difference, by specification: an entry
+    ``slot_mapping[t] < 0`` is padding and is skipped (the Triton kernel would
+    write out of bounds for it).
+    """
+    for n, t in (("key", key), ("value", value), ("key_cache", key_cache), ("value_cache", value_cache)):
+        _require_cuda(n, t)
+    dev = key_cache.device
+    k_tok, row_bytes = _row_layout("key", key)
+    v_tok, v_row = _row_layout("value", value)
+    if v_row != row_bytes or value.shape[0] != key.shape[0]:
+        raise ValueError("key and value must have the same shape")
+    if not (key_cache.is_contiguous() and value_cache.is_contiguous()):
+        raise ValueError("key_cache and value_cache must be contiguous")
+    if key.dtype != key_cache.dtype or value.dtype != value_cache.dtype:
+        raise TypeError("cache dtype must match key/value dtype (bytes are copied, not converted)")
+    if slot_mapping.numel() != key.shape[0]:
+        raise ValueError("slot_mapping must have one entry per token")
+    slots = _slots_i64(slot_mapping, dev)
+    num_slots = key_cache.numel() * key_cache.element_size() // row_bytes
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().lms_reshape_and_cache(
+            key.data_ptr(), value.data_ptr(), k_tok, v_tok,
+            key_cache.data_ptr(), value_cache.data_ptr(),
+            row_bytes, row_bytes,  # block_stride with block_size 1: flat slots
+            slots.data_ptr(), key.shape[0], row_bytes, 1, num_slots,
+            _stream_ptr(dev)))
+
+
+def reshape_and_cache(
+    key: torch.Tensor,
+    value: torch.Tensor,
+    kv_cache: torch.Tensor,
+    slot_mapping: torch.Tensor,
+) -> None:
+    """Writes ``key``/``value`` ``[T, H, D]`` into one layer's interleaved paged cache.
+
+    ``kv_cache`` is ``kv_caches[layer]`` = ``[num_blocks, 2, block_size, H, D]``
+    (``model_worker.py:221-228``); token ``t`` goes to block
+    ``slot // block_size``, entry ``slot % block_size``, K in plane 0 and V in
+    plane 1 — the addressing ``flashinfer.append_paged_kv_cache`` performs at
+    ``models/layers/attention.py:76-85`` with
+    ``slot = block_table[pos // block_size] * block_size + pos % block_size``.
+    Entries ``< 0`` are skipped.
+    """
+    _write_layers(key.unsqueeze(0) if key.dim() == 3 else key,
+                  value.unsqueeze(0) if value.dim() == 3 else value,
+                  kv_cache.unsqueeze(0) if kv_cache.dim() == 5 else kv_cache,
+                  slot_mapping)
+
+
+def reshape_and_cache_layers(
+    key: torch.Tensor,
+    value: torch.Tensor,
+    kv_caches: torch.Tensor,
+    slot_mapping: torch.Tensor,
+) -> None:
+    """All layers of one step in a single launch.
+
+    ``key``/``value``: ``[L, T, H, D]``; ``kv_caches``: the whole
+    ``[L, num_blocks, 2, block_size, H, D]`` tensor; ``slot_mapping``: ``[T]``
+    (shared by every layer, as the block tables are in LMServe) or ``[L, T]``.
+    """
+    _write_layers(key, value, kv_caches, slot_mapping)
+
+
+def _write_layers(key, value, kv_caches, slot_mapping) -> None:
+    for n, t in (("key", key), ("value", value), ("kv_caches", kv_caches)):
+        _require_cuda(n, t)
+    if key.dim() != 4 or value.dim() != 4 or key.shape != value.shape:
+        raise ValueError("key and value must both be [L, T, H, D] (or [T, H, D] for one layer)")
+    if kv_caches.dim() != 6 or kv_caches.shape[2] != 2:
+        raise ValueError("kv cache must be [L, num_blocks, 2, block_size, H, D]")
+    L, NB, _, BS, H, D = kv_caches.shape
+    if key.shape[0] != L or tuple(key.shape[2:]) != (H, D):
+        raise ValueError(f"key {tuple(key.shape)} does not match cache {tuple(kv_caches.shape)}")
+    if key.dtype != kv_caches.dtype or value.dtype != kv_caches.dtype:
+        raise TypeError("cache dtype must match key/value dtype (bytes are copied, not converted)")
+    es = kv_caches.element_size()
+    if NB > 0 and L > 0 and not kv_caches[0, 0].is_contiguous():
+        raise ValueError("each cache block [2, block_size, H, D] must be contiguous")
+    dev = kv_caches.device
+    T = key.shape[1]
+    k_tok, row_bytes = _row_layout("key", key[0])
+    v_tok, _ = _row_layout("value", value[0])
+    slots = _slots_i64(slot_mapping, dev)
+    if slots.dim() == 1 and slots.shape[0] == T:
+        slot_layer = 0
+    elif slots.dim() == 2 and tuple(slots.shape) == (L, T):
+        slot_layer = T
+    else:
+        raise ValueError(f"slot_mapping must be [T] or [L, T], got {tuple(slots.shape)}")
+    kbase = kv_caches.data_ptr()
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().lms_reshape_and_cache_layers(
+            key.data_ptr(), value.data_ptr(), k_tok, v_tok,
+            key.stride(0) * es, value.stride(0) * es,
+            kbase, kbase + BS * row_bytes,
+            kv_caches.stride(0) * es, kv_caches.stride(1) * es, row_bytes,
+            slots.data_ptr(), slot_layer, T, L, row_bytes, BS, NB * BS,
+            _stream_ptr(dev)))
+
+
+# --------------------------------------------------------------------- copies
+def _cache_geometry(kv_caches: torch.Tensor) -> Tuple[int, int, int, int, int]:
+    """(num_layers, num_blocks, layer stride, block stride, chunk bytes) of a layer-major cache."""
+    if kv_caches.dim() < 3:
+        raise ValueError("kv_caches must be [num_layers, num_blocks, ...]")
+    L, NB = kv_caches.shape[0], kv_caches.shape[1]
+    es = kv_caches.element_size()
+    chunk = kv_caches[0, 0].numel() * es
+    if not kv_caches[0, 0].is_contiguous():
+        raise ValueError("each (layer, block) chunk of the cache must be contiguous")
+    return L, NB, kv_caches.stride(0) * es, kv_caches.stride(1) * es, chunk
+
+
+def copy_blocks(
+    kv_caches: torch.Tensor,
+    src_to_dst: Union[Dict[int, List[int]], PairList],
+) -> None:
+    """Copy-on-write: ``kv_caches[:, dst] = kv_caches[:, src]`` for every mapped pair, in place.
+
+    Same contract as LMServe's ``copy_blocks`` (``ops/cache_ops.py:8-36``,
+    kernel ``ops/triton/cache_kernels.py:5-36``): ``kv_caches`` is
+    ``[L, num_blocks, 2, block_size, H, D]`` and ``src_to_dst`` maps a source
+    block to the list of blocks that receive a copy, in every layer.  A sequence
+    of ``(src, dst)`` pairs or an int64 ``[n, 2]`` tensor is accepted as well.
+    Destinations must be distinct and must not also appear as sources.
+    """
+    _require_cuda("kv_caches", kv_caches)
+    dev = kv_caches.device
+    L, NB, layer_stride, block_stride, chunk = _cache_geometry(kv_caches)
+    pairs = _pairs_on_device(src_to_dst, dev)
+    n = pairs.shape[0]
+    if n == 0:
+        return
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().lms_copy_blocks(
+            kv_caches.data_ptr(), layer_stride, block_stride, chunk, L,
+            pairs.data_ptr(), n, NB, _stream_ptr(dev)))
+
+
+def swap_blocks(
+    gpu_kv_caches: torch.Tensor,
+    host_pool,
+    block_pairs: PairList,
+    direction: str,
+    layers: Optional[Tuple[int, int]] = None,
+) -> None:
+    """Moves whole blocks between the GPU cache and a pinned host pool.
+
+    ``gpu_kv_caches``: ``[L, num_gpu_blocks, ...]`` (layer-major);
+    ``host_pool``: a :class:`lmserve_b200.kv_worker.HostPool`
+    (``[num_host_blocks, L, chunk]``, block-major — ``kv_worker.py:123-130``);
+    ``direction``: ``"out"`` copies ``gpu[l, src] -> host[dst, l]``
+    (``kv_worker.py:213-227``), ``"in"`` copies ``host[src, l] -> gpu[l, dst]``
+    (``kv_worker.py:197-211``); ``layers=(begin, end)`` restricts the call to a
+    layer range so a caller can pipeline the swap against the forward pass.
+    """
+    _require_cuda("gpu_kv_caches", gpu_kv_caches)
+    if direction not in ("out", "in"):
+        raise ValueError(f"Unsupported copy direction: {direction!r} (use 'out' or 'in')")
+    dev = gpu_kv_caches.device
+    L, NB, layer_stride, block_stride, chunk = _cache_geometry(gpu_kv_caches)
+    if host_pool.num_layers != L or host_pool.chunk_bytes != chunk:
+        raise ValueError("host pool geometry does not match the GPU cache")
+    l0, l1 = (0, L) if layers is None else layers
+    if not (0 <= l0 <= l1 <= L):
+        raise ValueError(f"layer range {layers} outside [0, {L}]")
+    pairs = _pairs_on_device(block_pairs, dev)
+    n = pairs.shape[0]
+    if n == 0 or l0 == l1:
+        return
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().lms_swap_blocks(
+            _lib.LMS_SWAP_OUT if direction == "out" else _lib.LMS_SWAP_IN,
+            gpu_kv_caches.data_ptr(), layer_stride, block_stride,
+            host_pool.device_ptr, host_pool.block_stride, host_pool.layer_stride,
+            chunk, l0, l1, pairs.data_ptr(), n, NB, host_pool.num_blocks,
+            _stream_ptr(dev)))
+
+
+def transfer_blocks(
+    src_kv_caches: torch.Tensor,
+    dst_kv_caches,
+    block_pairs: PairList,
+) -> None:
+    """Pushes blocks of the local cache into a peer GPU's cache: ``dst[:, d] = src[:, s]``.
+
+    Replaces the host-staged NIXL push of ``kv_worker.py:358-415`` with one
+    kernel on the source GPU storing over NVLink.  ``dst_kv_caches`` is either a
+    tensor on another device of this process (peer access is enabled on demand)
+    or a :class:`lmserve_b200.kv_worker.PeerCache` opened from another
+    process's IPC handle.  Runs on the source device's current stream.
+    """
+    _require_cuda("src_kv_caches", src_kv_caches)
+    dev = src_kv_caches.device
+    L, NB, s_layer, s_block, chunk = _cache_geometry(src_kv_caches)
+    if isinstance(dst_kv_caches, torch.Tensor):
+        _require_cuda("dst_kv_caches", dst_kv_caches)
+        dL, dNB, d_layer, d_block, d_chunk = _cache_geometry(dst_kv_caches)
+        dst_ptr = dst_kv_caches.data_ptr()
+        if dst_kv_caches.device != dev:
+            with torch.cuda.device(dev):
+                _lib.check(_lib.lib().lms_peer_enable(dst_kv_caches.device.index))
+    else:
+        dL, dNB, d_layer, d_block, d_chunk = (dst_kv_caches.num_layers, dst_kv_caches.num_blocks,
+                                              dst_kv_caches.layer_stride, dst_kv_caches.block_stride,
+                                              dst_kv_caches.chunk_bytes)
+        dst_ptr = dst_kv_caches.device_ptr
+    if dL != L or d_chunk != chunk:
+        raise ValueError("source and destination caches must have the same layers and chunk size")
+    pairs = _pairs_on_device(block_pairs, dev)
+    n = pairs.shape[0]
+    if n == 0:
+        return
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().lms_transfer_blocks(
+            src_kv_caches.data_ptr(), s_layer, s_block, dst_ptr, d_layer, d_block,
+            chunk, L, pairs.data_ptr(), n, NB, dNB, _stream_ptr(dev)))

@@ -1,0 +1,15 @@
+"""CPU oracle of the KV-cache data-movement path.  TEST INFRASTRUCTURE ONLY.
+
+Nothing in ``lmserve_b200`` imports this package.  It may be imported by
+``tests/``, by ``__graft_entry__.smoke()`` and by ``bench.py``'s CPU-baseline /
+reference arm, always as the checker or the timed baseline and never as a data
+path of the product.
+
+Parity pin: LMServe ships no tests, golden vectors or fixtures for this path, so
+the oracle is pinned against LMServe's own Triton cache kernels
+(``runtime/worker/llm_worker/ops/triton/cache_kernels.py``) executed on CPU with
+the Triton interpreter; the outputs are committed under ``tests/golden/`` together
+with ``tests/golden/make_golden.py`` that produced them.  The swap and transfer
+restatements have no executable reference (pycuda / NIXL are not installable
+here) and follow ``kv_worker.py`` by reading: for those two, parity is unpinned.
+"""

@@ -1,0 +1,328 @@
+"""GPU: every cache op, called through the C ABI, against the CPU oracle — bit-exact.
+
+Covers the golden vectors made by LMServe's own kernels, the full-size plumbing case, scaled
+versions of the decode / chunked-prefill / TP-sharded workloads in every kernel variant, and
+the edge cases: empty input, all-padding, single token, last slot of the pool, row and block
+sizes that are not powers of two, strided inputs, guard regions around the cache, block
+strides beyond 2^31 elements, and out-of-range indices under debug checks."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import COPY_CASES, FILL_CASES, load_json, load_npz, sha, to_tensor, to_words
+from lmserve_b200 import _lib, workloads as W
+from lmserve_b200.ops import cache_ops
+from oracle import cache_oracle
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+VARIANTS = [0, 1, 2]  # 16-byte vectors, 32-byte vectors, bulk (TMA) copies
+
+
+@pytest.fixture(autouse=True)
+def _reset_tuning():
+    yield
+    L = _lib.lib()
+    for key in range(1, 9):
+        L.lms_set_tuning(key, -1)
+    L.lms_set_debug_checks(0)
+
+
+def set_variant(v):
+    L = _lib.lib()
+    for key in (_lib.TUNE_WRITE_VARIANT, _lib.TUNE_COPY_VARIANT, _lib.TUNE_XFER_VARIANT):
+        assert L.lms_set_tuning(key, v) == 0
+
+
+# ----------------------------------------------------------------- golden vectors
+@pytest.mark.parametrize("variant", VARIANTS)
+@pytest.mark.parametrize("name", FILL_CASES)
+def test_fill_key_cache_golden(name, variant):
+    set_variant(variant)
+    g = load_npz(name)
+    dt = g["dtype"]
+    kc, vc = to_tensor(g["key_cache_in"], dt, DEV), to_tensor(g["value_cache_in"], dt, DEV)
+    before = _lib.lib().lms_launch_count()
+    cache_ops.fill_key_cache(to_tensor(g["key"], dt, DEV), to_tensor(g["value"], dt, DEV), kc, vc,
+                             torch.from_numpy(g["slot_mapping"]).to(DEV))
+    torch.cuda.synchronize()
+    assert _lib.lib().lms_launch_count() == before + 1
+    assert np.array_equal(to_words(kc), g["key_cache_out"])
+    assert np.array_equal(to_words(vc), g["value_cache_out"])
+
+
+@pytest.mark.parametrize("variant", VARIANTS)
+@pytest.mark.parametrize("name", COPY_CASES)
+def test_copy_blocks_golden(name, variant):
+    set_variant(variant)
+    g = load_npz(name)
+    kv = to_tensor(g["kv_in"], g["dtype"], DEV)
+    d = {}
+    for s, dst in g["pairs"]:
+        d.setdefault(int(s), []).append(int(dst))
+    cache_ops.copy_blocks(kv, d)
+    torch.cuda.synchronize()
+    assert np.array_equal(to_words(kv), g["kv_out"])
+
+
+@pytest.mark.parametrize("variant", VARIANTS)
+def test_plumbing_case_full_size(variant):
+    """Llama-3.2-1B shape, 256 tokens with 16 padded slots, 64 block pairs: digests of the
+    outputs equal those of the reference kernels; padding is skipped."""
+    set_variant(variant)
+    g = load_json("plumbing_llama32_1b")
+    case = W.config1()
+    pay = W.plumbing_payload(case)
+    dt = case.shape.dtype
+    slots = torch.from_numpy(case.slot_mapping).to(DEV)
+    kc, vc = to_tensor(pay["key_cache"], dt, DEV), to_tensor(pay["value_cache"], dt, DEV)
+    key, value = to_tensor(pay["key"], dt, DEV), to_tensor(pay["value"], dt, DEV)
+    cache_ops.fill_key_cache(key, value, kc, vc, slots)
+    kv = to_tensor(pay["kv_caches"], dt, DEV)
+    cache_ops.copy_blocks(kv, case.pairs)
+    torch.cuda.synchronize()
+    assert sha(to_words(kc)) == g["outputs"]["key_cache"]
+    assert sha(to_words(vc)) == g["outputs"]["value_cache"]
+    assert sha(to_words(kv)) == g["outputs"]["kv_caches"]
+    # the interleaved layout of the same case, against the oracle
+    kv2 = to_tensor(pay["kv_caches"], dt, DEV)
+    cache_ops.reshape_and_cache(key, value, kv2[0], slots)
+    want = pay["kv_caches"].copy()
+    cache_oracle.reshape_and_cache(pay["key"], pay["value"], want[0], case.slot_mapping)
+    torch.cuda.synchronize()
+    assert np.array_equal(to_words(kv2), want)
+
+
+# ----------------------------------------------------------------- multi-layer writes
+def run_layers_case(shape, slots_np, seed, slot_per_layer=False):
+    rng = np.random.default_rng(seed)
+    L, T = shape.num_layers, len(slots_np)
+    key = W.normal_words(rng, (L, T, shape.num_kv_heads, shape.head_dim), shape.dtype)
+    value = W.normal_words(rng, (L, T, shape.num_kv_heads, shape.head_dim), shape.dtype)
+    cache = W.normal_words(rng, shape.cache_shape, shape.dtype)
+    if slot_per_layer:
+        slots_np = np.stack([np.roll(slots_np, l) for l in range(L)])
+    want = cache.copy()
+    cache_oracle.reshape_and_cache_layers(key, value, want, slots_np)
+    got = to_tensor(cache, shape.dtype, DEV)
+    cache_ops.reshape_and_cache_layers(to_tensor(key, shape.dtype, DEV),
+                                       to_tensor(value, shape.dtype, DEV), got,
+                                       torch.from_numpy(slots_np).to(DEV))
+    torch.cuda.synchronize()
+    assert np.array_equal(to_words(got), want)
+
+
+@pytest.mark.parametrize("variant", VARIANTS)
+def test_decode_write_scaled(variant):
+    set_variant(variant)
+    shape = W.SHAPES["llama31_8b"].scaled(num_layers=4, num_blocks=512)
+    w = W.make_decode_write(shape, 48, 16, 160, seed=31)
+    run_layers_case(shape, w.slot_mapping, 41)
+    run_layers_case(shape, w.slot_mapping, 42, slot_per_layer=True)
+
+
+@pytest.mark.parametrize("variant", VARIANTS)
+def test_chunked_prefill_scaled(variant):
+    set_variant(variant)
+    shape = W.SHAPES["qwen25_7b"].scaled(num_layers=3, num_blocks=1024)
+    w = W.make_prefill_cow(shape, 6, 200, 1500, 4, 8, seed=33)
+    slots = w.slot_mapping.copy()
+    slots[::37] = -1
+    run_layers_case(shape, slots, 43)
+
+
+@pytest.mark.parametrize("variant", VARIANTS)
+def test_tp_sharded_decode_write_scaled(variant):
+    """One KV head per GPU (256-byte rows), the TP=8 shape."""
+    set_variant(variant)
+    shape = W.SHAPES["llama31_70b_tp8"].scaled(num_layers=5, num_blocks=2048)
+    w = W.make_decode_write(shape, 100, 64, 300, seed=35)
+    run_layers_case(shape, w.slot_mapping, 45)
+
+
+@pytest.mark.parametrize("variant", VARIANTS)
+@pytest.mark.parametrize("tile", [0, 2048, 1 << 20])
+def test_write_tile_sizes(variant, tile):
+    set_variant(variant)
+    _lib.lib().lms_set_tuning(_lib.TUNE_WRITE_TILE_BYTES, tile)
+    shape = W.SHAPES["llama31_8b"].scaled(num_layers=2, num_blocks=64)
+    w = W.make_decode_write(shape, 37, 8, 200, seed=36)
+    run_layers_case(shape, w.slot_mapping, 46)
+
+
+# ----------------------------------------------------------------- edge cases
+@pytest.mark.parametrize("variant", VARIANTS)
+@pytest.mark.parametrize("H,D,BS", [(3, 8, 12), (1, 8, 16), (5, 24, 7), (3, 256, 16)])
+def test_odd_geometries(variant, H, D, BS):
+    """Rows of 48 / 16 / 240 / 1536 bytes, block sizes that are not powers of two."""
+    set_variant(variant)
+    shape = W.KVShape("odd", 2, H, D, "fp16", 9, BS)
+    rng = np.random.default_rng(7)
+    slots = rng.permutation(9 * BS)[:20].astype(np.int64)
+    slots[[2, 11]] = -1
+    slots[0] = 9 * BS - 1  # the last slot of the pool
+    run_layers_case(shape, slots, 47)
+
+
+@pytest.mark.parametrize("variant", VARIANTS)
+def test_empty_all_padding_and_single_token(variant):
+    set_variant(variant)
+    shape = W.KVShape("tiny", 2, 2, 64, "bf16", 8)
+    for slots in (np.empty(0, np.int64), np.full(5, -1, np.int64), np.array([77], np.int64)):
+        run_layers_case(shape, slots, 48)
+    kv = torch.randn(2, 8, 2, 16, 2, 64, device=DEV).to(torch.bfloat16)
+    ref = kv.clone()
+    cache_ops.copy_blocks(kv, {})
+    cache_ops.copy_blocks(kv, np.empty((0, 2), np.int64))
+    torch.cuda.synchronize()
+    assert torch.equal(kv.view(torch.int16), ref.view(torch.int16))
+
+
+@pytest.mark.parametrize("variant", VARIANTS)
+def test_strided_key_value_and_guard_regions(variant):
+    """key/value are slices of a fused qkv projection (token stride > row); the cache is a
+    slice of a larger buffer whose guard blocks on both sides must stay untouched."""
+    set_variant(variant)
+    T, H, D, BS, NB = 33, 4, 64, 16, 10
+    rng = np.random.default_rng(8)
+    qkv = to_tensor(W.normal_words(rng, (T, 3 * H * D), "bf16"), "bf16", DEV)
+    key = qkv[:, H * D:2 * H * D].view(T, H, D)
+    value = qkv[:, 2 * H * D:].view(T, H, D)
+    big_words = W.normal_words(rng, (NB + 4, 2, BS, H, D), "bf16")
+    big = to_tensor(big_words, "bf16", DEV)
+    cache = big[2:NB + 2]
+    slots = rng.permutation(NB * BS)[:T].astype(np.int64)
+    slots[5] = -1
+    slots[0], slots[1] = 0, NB * BS - 1  # first and last slot, next to the guards
+    cache_ops.reshape_and_cache(key, value, cache, torch.from_numpy(slots).to(DEV))
+    want = big_words.copy()
+    cache_oracle.reshape_and_cache(to_words(key), to_words(value), want[2:NB + 2], slots)
+    torch.cuda.synchronize()
+    got = to_words(big)
+    assert np.array_equal(got[:2], big_words[:2]) and np.array_equal(got[NB + 2:], big_words[NB + 2:])
+    assert np.array_equal(got, want)
+
+
+def test_int32_slot_mapping_is_accepted():
+    g = load_npz("fill_fp16_t8")
+    kc, vc = to_tensor(g["key_cache_in"], "fp16", DEV), to_tensor(g["value_cache_in"], "fp16", DEV)
+    cache_ops.fill_key_cache(to_tensor(g["key"], "fp16", DEV), to_tensor(g["value"], "fp16", DEV),
+                             kc, vc, torch.from_numpy(g["slot_mapping"].astype(np.int32)).to(DEV))
+    torch.cuda.synchronize()
+    assert np.array_equal(to_words(kc), g["key_cache_out"])
+
+
+@pytest.mark.parametrize("variant", VARIANTS)
+def test_block_stride_beyond_2_31_elements(variant):
+    """Two cache blocks 2.5 Gi elements apart inside one 5.1 GiB buffer: offsets need 64 bits."""
+    set_variant(variant)
+    H, D, BS, T = 8, 128, 16, 24
+    far = 5 * (1 << 29)  # elements between the two blocks (2.5 Gi)
+    buf = torch.zeros(far + 2 * BS * H * D + 64, dtype=torch.bfloat16, device=DEV)
+    cache = torch.as_strided(buf, (1, 2, 2, BS, H, D),
+                             (far * 2, far, BS * H * D, H * D, D, 1))
+    rng = np.random.default_rng(10)
+    key_w, val_w = W.normal_words(rng, (T, H, D), "bf16"), W.normal_words(rng, (T, H, D), "bf16")
+    slots = np.concatenate([np.arange(0, 12), BS + np.arange(4, 16)]).astype(np.int64)
+    cache_ops.reshape_and_cache_layers(to_tensor(key_w, "bf16", DEV)[None],
+                                       to_tensor(val_w, "bf16", DEV)[None], cache,
+                                       torch.from_numpy(slots).to(DEV))
+    torch.cuda.synchronize()
+    want = np.zeros((2, 2, BS, H, D), np.uint16)
+    cache_oracle.reshape_and_cache(key_w, val_w, want, slots)
+    got = to_words(cache[0].contiguous())
+    assert np.array_equal(got, want)
+    # nothing landed where a 32-bit wrap of the far block's offset would point
+    wrapped = (far * 2) % (1 << 32) // 2
+    assert not buf[wrapped:wrapped + 2 * BS * H * D].view(torch.int16).any()
+    # copy_blocks across the same distance
+    kv3 = torch.as_strided(buf, (1, 2, 2 * BS * H * D), (far * 2, far, 1))
+    cache_ops.copy_blocks(kv3, [(1, 0)])
+    torch.cuda.synchronize()
+    assert np.array_equal(to_words(kv3[0, 0]), want[1].reshape(-1))
+
+
+# ----------------------------------------------------------------- copy-on-write
+@pytest.mark.parametrize("variant", VARIANTS)
+@pytest.mark.parametrize("per_sm", [0, 1, 16])
+def test_copy_blocks_fanout_scaled(variant, per_sm):
+    set_variant(variant)
+    _lib.lib().lms_set_tuning(_lib.TUNE_COPY_CTAS_PER_SM, per_sm)
+    shape = W.SHAPES["qwen25_7b"].scaled(num_layers=3, num_blocks=700)
+    w = W.make_prefill_cow(shape, 4, 100, 900, 5, 40, seed=51)
+    words = W.normal_words(np.random.default_rng(52), shape.cache_shape, shape.dtype)
+    kv = to_tensor(words, shape.dtype, DEV)
+    cache_ops.copy_blocks(kv, w.pairs)
+    want = words.copy()
+    cache_oracle.copy_blocks(want, w.pairs)
+    torch.cuda.synchronize()
+    assert np.array_equal(to_words(kv), want)
+
+
+@pytest.mark.parametrize("variant", VARIANTS)
+def test_copy_blocks_odd_chunk_and_many_pairs(variant):
+    """Chunk of 48 KiB + 16 bytes (not a multiple of the slice), more pairs than one staging round."""
+    set_variant(variant)
+    L, NB, chunk_words = 2, 900, (48 * 1024 + 16) // 2
+    rng = np.random.default_rng(53)
+    words = rng.integers(0, 2**16, size=(L, NB, chunk_words), dtype=np.uint16)
+    kv = to_tensor(words, "fp16", DEV)
+    perm = rng.permutation(NB)
+    pairs = np.stack([perm[:10].repeat(40), perm[10:410]], axis=1).astype(np.int64)
+    cache_ops.copy_blocks(kv, pairs)
+    want = words.copy()
+    cache_oracle.copy_blocks(want, pairs)
+    torch.cuda.synchronize()
+    assert np.array_equal(to_words(kv), want)
+
+
+# ----------------------------------------------------------------- debug checks
+def test_debug_checks_report_bad_slot_and_skip_it():
+    L = _lib.lib()
+    assert L.lms_set_debug_checks(1) == 0
+    T, H, D, NS = 6, 2, 32, 40
+    key = torch.randn(T, H, D, device=DEV).half()
+    kc = torch.zeros(NS, H, D, device=DEV).half()
+    vc = torch.zeros_like(kc)
+    guard = torch.zeros(64, H, D, device=DEV).half()  # likely neighbours in the allocator
+    slots = torch.tensor([0, 1, NS + 3, 5, -1, 7], device=DEV)
+    cache_ops.fill_key_cache(key, key, kc, vc, slots)
+    idx, val = ctypes.c_int64(-1), ctypes.c_int64(-1)
+    rc = L.lms_check_device_errors(None, ctypes.byref(idx), ctypes.byref(val))
+    assert rc == _lib.LMS_ERR_INDEX and idx.value == 2 and val.value == NS + 3
+    assert L.lms_check_device_errors(None, None, None) == 0  # cleared
+    assert torch.equal(kc[[0, 1, 5, 7]], key[[0, 1, 3, 5]])
+    assert not guard.any()
+    with pytest.raises(_lib.LmsError):
+        _lib.check(rc)
+
+
+def test_debug_checks_report_bad_block_pair():
+    L = _lib.lib()
+    L.lms_set_debug_checks(1)
+    kv = torch.randn(2, 6, 2, 4, 2, 16, device=DEV).half()
+    ref = kv.clone()
+    cache_ops.copy_blocks(kv, [(0, 1), (9, 2), (3, 4)])
+    idx, val = ctypes.c_int64(), ctypes.c_int64()
+    assert L.lms_check_device_errors(None, ctypes.byref(idx), ctypes.byref(val)) == _lib.LMS_ERR_INDEX
+    assert (idx.value, val.value) == (1, 9)
+    assert torch.equal(kv[:, 1], ref[:, 0]) and torch.equal(kv[:, 4], ref[:, 3])
+    assert torch.equal(kv[:, 2], ref[:, 2])
+    cache_ops.copy_blocks(kv, [(0, 7)])
+    assert L.lms_check_device_errors(None, ctypes.byref(idx), ctypes.byref(val)) == _lib.LMS_ERR_INDEX
+    assert (idx.value, val.value) == (0, 7)
+
+
+def test_runs_on_the_callers_stream():
+    s = torch.cuda.Stream()
+    g = load_npz("fill_bf16_t24")
+    kc, vc = to_tensor(g["key_cache_in"], "bf16", DEV), to_tensor(g["value_cache_in"], "bf16", DEV)
+    key, value = to_tensor(g["key"], "bf16", DEV), to_tensor(g["value"], "bf16", DEV)
+    slots = torch.from_numpy(g["slot_mapping"]).to(DEV)
+    torch.cuda.synchronize()
+    with torch.cuda.stream(s):
+        cache_ops.fill_key_cache(key, value, kc, vc, slots)
+    s.synchronize()
+    assert np.array_equal(to_words(kc), g["key_cache_out"])

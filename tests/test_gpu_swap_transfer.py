@@ -1,0 +1,189 @@
+"""GPU: GPU<->pinned-host swap and prefill->decode transfer against the oracle, through the
+C ABI and through the KVWorker mirror (events per layer, descriptors, push from another
+process)."""
+import multiprocessing as mp
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import to_tensor, to_words
+from lmserve_b200 import _lib, workloads as W
+from lmserve_b200.kv_worker import BlockMapping, Device, HostPool, KVWorker
+from lmserve_b200.ops import cache_ops
+from oracle import cache_oracle
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+@pytest.fixture(autouse=True)
+def _reset_tuning():
+    yield
+    for key in range(1, 9):
+        _lib.lib().lms_set_tuning(key, -1)
+
+
+def make_gpu_cache(shape, seed):
+    words = W.normal_words(np.random.default_rng(seed), shape.cache_shape, shape.dtype)
+    return words, to_tensor(words, shape.dtype, DEV)
+
+
+@pytest.mark.parametrize("ctas", [0, 8, 300])
+def test_swap_out_in_vs_oracle(ctas):
+    L = _lib.lib()
+    L.lms_set_tuning(_lib.TUNE_SWAP_OUT_CTAS, ctas)
+    L.lms_set_tuning(_lib.TUNE_SWAP_IN_CTAS, ctas)
+    shape = W.SHAPES["llama31_8b_swap"].scaled(num_layers=3, num_blocks=64)
+    sw = W.make_swap(shape, num_host_blocks=40, n_blocks=20, seed=61)
+    words, gpu = make_gpu_cache(shape, 62)
+    pool = HostPool(40, shape.num_layers, shape.chunk_bytes)
+    try:
+        rng = np.random.default_rng(63)
+        pool.array[...] = rng.integers(0, 256, size=pool.array.shape, dtype=np.uint8)
+        host_want = pool.array.copy().view(np.uint16)
+        gpu_want = words.reshape(shape.num_layers, shape.num_blocks, -1).copy()
+        cache_ops.swap_blocks(gpu, pool, sw.out_pairs, "out")
+        torch.cuda.synchronize()
+        cache_oracle.swap_out(gpu_want, host_want, sw.out_pairs)
+        assert np.array_equal(pool.array.view(np.uint16), host_want)
+        cache_ops.swap_blocks(gpu, pool, sw.in_pairs, "in")
+        torch.cuda.synchronize()
+        cache_oracle.swap_in(gpu_want, host_want, sw.in_pairs)
+        got = to_words(gpu).reshape(gpu_want.shape)
+        assert np.array_equal(got, gpu_want)
+        # round trip: every swapped-in block equals the block that was swapped out
+        back = {int(h): int(g) for g, h in sw.out_pairs}
+        for h, d in sw.in_pairs:
+            assert np.array_equal(got[:, d], got[:, back[int(h)]])
+    finally:
+        pool.close()
+
+
+def test_swap_layer_range_and_empty():
+    shape = W.SHAPES["llama31_8b_swap"].scaled(num_layers=4, num_blocks=16, num_kv_heads=2)
+    words, gpu = make_gpu_cache(shape, 64)
+    pool = HostPool(8, 4, shape.chunk_bytes)
+    try:
+        pool.array[...] = 0
+        pairs = np.array([[3, 1], [15, 7], [0, 0]], dtype=np.int64)
+        cache_ops.swap_blocks(gpu, pool, pairs, "out", layers=(1, 3))
+        cache_ops.swap_blocks(gpu, pool, np.empty((0, 2), np.int64), "out")
+        cache_ops.swap_blocks(gpu, pool, pairs, "out", layers=(2, 2))
+        torch.cuda.synchronize()
+        want = np.zeros((8, 4, shape.chunk_bytes // 2), np.uint16)
+        cache_oracle.swap_out(words.reshape(4, 16, -1), want, pairs, layers=(1, 3))
+        assert np.array_equal(pool.array.view(np.uint16), want)
+        with pytest.raises(ValueError, match="Unsupported copy direction"):
+            cache_ops.swap_blocks(gpu, pool, pairs, "sideways")
+        with pytest.raises(ValueError):
+            cache_ops.swap_blocks(gpu, pool, pairs, "out", layers=(3, 9))
+    finally:
+        pool.close()
+
+
+def test_kvworker_copy_kv_with_layer_events():
+    """Write-through then fetch, one launch per layer, ordered by per-layer events the way the
+    model's forward hooks and the KV worker hand layers to each other."""
+    shape = W.SHAPES["llama31_8b_swap"].scaled(num_layers=4, num_blocks=32, num_kv_heads=2)
+    words, gpu = make_gpu_cache(shape, 65)
+    worker = KVWorker("kv0", gpu, num_host_blocks=16)
+    try:
+        sw = W.make_swap(shape, 16, 10, seed=66)
+        maps_out = [BlockMapping.from_pairs(sw.out_pairs[:4]), BlockMapping.from_pairs(sw.out_pairs[4:])]
+        post = [torch.cuda.Event() for _ in range(4)]
+        for e in post:
+            e.record(torch.cuda.current_stream())
+        worker.copy_kv(maps_out, Device.GPU, Device.Host, post_events=post)
+        worker.dtoh_stream.synchronize()
+        pre = [torch.cuda.Event() for _ in range(4)]
+        worker.copy_kv([sw.in_pairs], Device.Host, Device.GPU, pre_events=pre, layers_per_launch=2)
+        for e in pre:
+            torch.cuda.current_stream().wait_event(e)
+        torch.cuda.synchronize()
+        gpu_want = words.reshape(4, 32, -1).copy()
+        host_want = np.zeros((16, 4, shape.chunk_bytes // 2), np.uint16)
+        cache_oracle.swap_out(gpu_want, host_want, sw.out_pairs)
+        cache_oracle.swap_in(gpu_want, host_want, sw.in_pairs)
+        assert np.array_equal(to_words(gpu).reshape(gpu_want.shape), gpu_want)
+        with pytest.raises(ValueError, match="Unsupported copy direction"):
+            worker.copy_kv([], Device.Host, Device.Disk)
+    finally:
+        worker.close()
+
+
+@pytest.mark.parametrize("variant", [0, 1, 2])
+def test_transfer_blocks_same_device_vs_oracle(variant):
+    _lib.lib().lms_set_tuning(_lib.TUNE_XFER_VARIANT, variant)
+    shape = W.SHAPES["llama31_70b_tp8"].scaled(num_layers=6, num_blocks=300)
+    tr = W.make_transfer(shape, 4, 300, seed=71, dst_num_blocks=200)
+    src_words, src = make_gpu_cache(shape, 72)
+    dshape = shape.scaled(num_blocks=200)
+    dst_words, dst = make_gpu_cache(dshape, 73)
+    cache_ops.transfer_blocks(src, dst, tr.pairs)
+    torch.cuda.synchronize()
+    want = dst_words.copy()
+    cache_oracle.transfer(src_words, want, tr.pairs)
+    assert np.array_equal(to_words(dst), want)
+    assert np.array_equal(to_words(src), src_words)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_transfer_blocks_across_devices():
+    shape = W.SHAPES["llama31_70b_tp8"].scaled(num_layers=4, num_blocks=128)
+    tr = W.make_transfer(shape, 3, 400, seed=74)
+    src_words, src = make_gpu_cache(shape, 75)
+    dst_words = W.normal_words(np.random.default_rng(76), shape.cache_shape, shape.dtype)
+    dst = to_tensor(dst_words, shape.dtype, "cuda:1")
+    torch.cuda.synchronize("cuda:1")
+    cache_ops.transfer_blocks(src, dst, tr.pairs)
+    torch.cuda.synchronize("cuda:0")
+    want = dst_words.copy()
+    cache_oracle.transfer(src_words, want, tr.pairs)
+    assert np.array_equal(to_words(dst), want)
+
+
+def _pusher(desc_bytes, seed, pairs_src, q):
+    """Child process = the prefill-side worker: builds its own cache and pushes blocks into the
+    parent's cache through the IPC descriptor."""
+    try:
+        import numpy as np
+        import torch
+        from helpers import to_tensor
+        from lmserve_b200 import workloads as W
+        from lmserve_b200.kv_worker import KVWorker
+        shape = W.SHAPES["llama31_70b_tp8"].scaled(num_layers=4, num_blocks=64)
+        words = W.normal_words(np.random.default_rng(seed), shape.cache_shape, shape.dtype)
+        cache = to_tensor(words, shape.dtype, "cuda:0")
+        w = KVWorker("prefill0", cache)
+        ok = w.push_kv("decode0", desc_bytes, pairs_src)
+        w.push_stream.synchronize()
+        w.close()
+        q.put(("ok", ok))
+    except Exception as e:  # pragma: no cover - reported to the parent
+        q.put(("error", repr(e)))
+
+
+def test_push_kv_from_another_process():
+    """get_descriptors on the decode side, push_kv from a second process (CUDA IPC mapping of
+    the destination cache), surplus remote blocks dropped as in the reference."""
+    shape = W.SHAPES["llama31_70b_tp8"].scaled(num_layers=4, num_blocks=64)
+    dst_words, dst = make_gpu_cache(shape, 81)
+    decode = KVWorker("decode0", dst)
+    reserved = [5, 9, 33, 2, 60, 61]          # two more than will be pushed
+    src_blocks = [7, 8, 40, 41]
+    desc = decode.get_descriptors(reserved)
+    torch.cuda.synchronize()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    p = ctx.Process(target=_pusher, args=(desc, 82, src_blocks, q))
+    p.start()
+    status, payload = q.get(timeout=300)
+    p.join(timeout=60)
+    assert status == "ok" and payload is True, payload
+    torch.cuda.synchronize()
+    src_words = W.normal_words(np.random.default_rng(82), shape.cache_shape, shape.dtype)
+    want = dst_words.copy()
+    cache_oracle.transfer(src_words, want, np.stack([src_blocks, reserved[:4]], axis=1))
+    assert np.array_equal(to_words(dst), want)
+    decode.close()

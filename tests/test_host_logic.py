@@ -1,0 +1,127 @@
+"""CPU: host-side logic around the kernels — block-map flattening, workload generators,
+the KVWorker mapping helpers, and the refusal to run on CPU tensors."""
+import numpy as np
+import pytest
+import torch
+
+from lmserve_b200 import workloads as W
+from lmserve_b200.kv_worker import (BlockMapping, BlockMappingEntry, CacheDescriptor, Device,
+                                    mappings_to_pairs)
+from lmserve_b200.ops import cache_ops
+from oracle import cache_oracle
+
+
+def test_flatten_block_map_matches_reference_order():
+    d = {7: [1, 2, 3], 4: [], 9: [0]}
+    got = cache_ops.flatten_block_map(d)
+    assert got.dtype == np.int64
+    assert got.tolist() == [[7, 1], [7, 2], [7, 3], [9, 0]]
+    assert np.array_equal(got, cache_oracle.flatten_block_map(d))
+    assert cache_ops.flatten_block_map({}).shape == (0, 2)
+    assert cache_ops.flatten_block_map([]).shape == (0, 2)
+    assert cache_ops.flatten_block_map([(1, 2), (3, 4)]).tolist() == [[1, 2], [3, 4]]
+    with pytest.raises(ValueError):
+        cache_ops.flatten_block_map([1, 2, 3])
+    with pytest.raises(TypeError):
+        cache_ops.flatten_block_map(np.zeros((2, 2), dtype=np.float32))
+
+
+def test_mappings_to_pairs():
+    ms = [BlockMapping([BlockMappingEntry(1, 2), BlockMappingEntry(3, 4)]), BlockMapping(),
+          BlockMapping.from_pairs([(5, 6)])]
+    assert mappings_to_pairs(ms).tolist() == [[1, 2], [3, 4], [5, 6]]
+    assert mappings_to_pairs([]).shape == (0, 2)
+    assert Device.GPU == 0 and Device.Host == 1 and Device.Disk == 2
+
+
+def test_ops_reject_cpu_tensors():
+    k = torch.zeros(4, 2, 8, dtype=torch.float16)
+    c = torch.zeros(16, 2, 8, dtype=torch.float16)
+    s = torch.arange(4)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        cache_ops.fill_key_cache(k, k, c, c, s)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        cache_ops.copy_blocks(torch.zeros(1, 4, 2, 2, 2, 8), {0: [1]})
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        cache_ops.reshape_and_cache(k, k, torch.zeros(4, 2, 4, 2, 8, dtype=torch.float16), s)
+
+
+def test_descriptor_roundtrip():
+    d = CacheDescriptor(b"\x01" * 64, 256, 3, 80, 1000, 1 << 23, 8192, 8192, [5, 9, 2])
+    e = CacheDescriptor.deserialize(d.serialize())
+    assert e == d
+
+
+@pytest.mark.parametrize("cfg", ["config2", "config5_decode"])
+def test_decode_write_workload_invariants(cfg):
+    w = getattr(W, cfg)()
+    s = w.shape
+    assert w.slot_mapping.dtype == np.int64
+    assert len(np.unique(w.slot_mapping)) == w.num_tokens           # distinct slots
+    assert w.slot_mapping.min() >= 0 and w.slot_mapping.max() < s.num_blocks * s.block_size
+    # slot = table[pos // BS] * BS + pos % BS with pos = context length
+    for t, c, sl in zip(w.tables.tables, w.context_lens, w.slot_mapping):
+        assert sl == t[c // s.block_size] * s.block_size + c % s.block_size
+        assert len(t) == (c + 1 + s.block_size - 1) // s.block_size
+    alloc = w.tables.allocated
+    assert len(np.unique(alloc)) == len(alloc)                      # no block dealt twice
+    assert not np.intersect1d(alloc, w.tables.free).size
+
+
+def test_config_sizes_match_the_specification():
+    assert W.config2().algorithmic_bytes() == 64 << 20
+    assert W.config2().algorithmic_bytes(layers=1) == 2 << 20
+    c3 = W.config3()
+    assert len(c3.slot_mapping) == 32768 and len(c3.pairs) == 4096
+    assert c3.write_bytes(layers=1) == 128 << 20
+    assert c3.cow_bytes() == (4096 + 32) * 28 * 32768
+    assert W.config4().bytes_per_direction() == 16 << 30
+    assert W.config5_decode().algorithmic_bytes() == 40 << 20
+    assert W.config5_transfer().bytes() == 2560 << 20
+    assert W.SHAPES["llama31_8b"].cache_bytes == 128 << 30
+    assert W.SHAPES["llama31_8b"].chunk_bytes == 65536
+
+
+def test_prefill_cow_workload_invariants():
+    w = W.config3()
+    s = w.shape
+    assert len(np.unique(w.slot_mapping)) == len(w.slot_mapping)
+    src, dst = w.pairs[:, 0], w.pairs[:, 1]
+    assert len(np.unique(dst)) == len(dst) == 4096
+    assert len(np.unique(src)) == 32
+    assert not np.intersect1d(src, dst).size
+    assert np.all(np.bincount(np.unique(src, return_inverse=True)[1]) == 128)
+    # destinations come from the free list, sources from allocated blocks
+    assert np.isin(src, w.tables.allocated).all() and np.isin(dst, w.tables.free).all()
+    # runs of consecutive slots inside a block
+    runs = np.diff(w.slot_mapping.reshape(64, 512), axis=1)
+    assert (runs == 1).mean() > 0.9
+
+
+def test_swap_and_transfer_workload_invariants():
+    w = W.config4(num_host_blocks=16384, n_blocks=1024)
+    assert len(np.unique(w.out_pairs[:, 0])) == 1024 and len(np.unique(w.out_pairs[:, 1])) == 1024
+    assert sorted(w.in_pairs[:, 0]) == sorted(w.out_pairs[:, 1])      # the same host blocks come back
+    assert not np.intersect1d(w.in_pairs[:, 1], w.out_pairs[:, 0]).size
+    t = W.config5_transfer()
+    assert len(t.pairs) == 4096 and len(np.unique(t.pairs[:, 1])) == 4096
+    assert [W.transfer_peer(r, 8) for r in (0, 3, 4, 7)] == [("prefill", 4), ("prefill", 7),
+                                                             ("decode", 0), ("decode", 3)]
+    assert W.transfer_peer(0, 2) == ("prefill", 1) and W.transfer_peer(1, 2) == ("decode", 0)
+    assert W.transfer_peer(0, 1) == ("none", None)
+
+
+def test_plumbing_case_matches_its_description():
+    c = W.config1()
+    assert len(c.slot_mapping) == 256 and int((c.slot_mapping < 0).sum()) == 16
+    live = c.slot_mapping[c.slot_mapping >= 0]
+    assert len(np.unique(live)) == 240
+    assert len(c.pairs) == 64 and len(np.unique(c.pairs[:, 1])) == 64
+    assert not np.intersect1d(c.pairs[:, 0], c.pairs[:, 1]).size
+
+
+def test_bf16_rounding_matches_torch():
+    x = np.random.default_rng(0).standard_normal(4096).astype(np.float32)
+    ours = W.f32_to_bf16_bits(x)
+    ref = torch.from_numpy(x).to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
+    assert np.array_equal(ours, ref)
