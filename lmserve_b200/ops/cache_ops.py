@@ -92,7 +92,9 @@ def _pairs_on_device(pairs, device: torch.device) -> torch.Tensor:
     if isinstance(pairs, torch.Tensor) and pairs.is_cuda:
         if pairs.dim() != 2 or pairs.shape[1] != 2:
             raise ValueError(f"block pairs must have shape [n, 2], got {tuple(pairs.shape)}")
-        return pairs.to(device=device, dtype=torch.int64).contiguous()
+        pairs = pairs.to(device=device, dtype=torch.int64).contiguous()
+        # the kernels read one (src, dst) couple per 16-byte load
+        return pairs if pairs.data_ptr() % 16 == 0 else pairs.clone()
     arr = flatten_block_map(pairs)
     if arr.shape[0] == 0:
         return torch.empty((0, 2), dtype=torch.int64, device=device)
