@@ -192,6 +192,38 @@ int lms_transfer_blocks(const void* src, int64_t src_layer_stride,
                         int64_t num_src_blocks, int64_t num_dst_blocks,
                         void* stream);
 
+/*
+ * The three chunk-copy operations with the (src, dst) table in HOST memory, which is where
+ * LMServe's callers have it: copy_blocks flattens a Python dict and uploads it
+ * (runtime/worker/llm_worker/ops/cache_ops.py:12-19) and the swap / push paths walk
+ * protobuf BlockMapping entries on the host (runtime/worker/llm_worker/kv_worker.py:204-211,
+ * 220-227,375-387).  The table is uploaded on `stream` into a per-device table buffer owned
+ * by the library (cudaMalloc, grown on demand, so do not make a call that has to grow it
+ * inside stream capture), then the same kernel runs.  Calls on different streams are ordered
+ * against each other through an event so that the shared buffer is never overwritten while a
+ * kernel still reads it.  `host_pairs` may be reused as soon as the call returns when it is
+ * pageable memory; page-locked memory must stay valid until `stream` has passed the call.
+ * All other arguments are those of the device-table entry points above.
+ */
+int lms_copy_blocks_host(void* kv, int64_t layer_stride, int64_t block_stride,
+                         int64_t chunk_bytes, int32_t num_layers,
+                         const int64_t* host_pairs, int64_t n_pairs,
+                         int64_t num_blocks, void* stream);
+int lms_swap_blocks_host(int direction, void* gpu, int64_t gpu_layer_stride,
+                         int64_t gpu_block_stride, void* host,
+                         int64_t host_block_stride, int64_t host_layer_stride,
+                         int64_t chunk_bytes, int32_t layer_begin, int32_t layer_end,
+                         const int64_t* host_pairs, int64_t n_pairs,
+                         int64_t num_gpu_blocks, int64_t num_host_blocks,
+                         void* stream);
+int lms_transfer_blocks_host(const void* src, int64_t src_layer_stride,
+                             int64_t src_block_stride, void* dst,
+                             int64_t dst_layer_stride, int64_t dst_block_stride,
+                             int64_t chunk_bytes, int32_t num_layers,
+                             const int64_t* host_pairs, int64_t n_pairs,
+                             int64_t num_src_blocks, int64_t num_dst_blocks,
+                             void* stream);
+
 /* Enables peer access from the current device to `peer_device`
  * (LMS_ERR_PEER when the two GPUs cannot reach each other). */
 int lms_peer_enable(int peer_device);

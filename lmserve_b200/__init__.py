@@ -7,9 +7,9 @@ All device work is done by ``liblmserve_kv.so`` (C ABI: ``include/lmserve_kv.h``
 """
 from . import _lib
 from .ops import (copy_blocks, fill_key_cache, reshape_and_cache,
-                  reshape_and_cache_layers, swap_blocks, transfer_blocks)
+                  reshape_and_cache_layers, swap_blocks, transfer_blocks, WritePlan)
 
 __version__ = "0.1.0"
 
 __all__ = ["copy_blocks", "fill_key_cache", "reshape_and_cache",
-           "reshape_and_cache_layers", "swap_blocks", "transfer_blocks", "_lib"]
+           "reshape_and_cache_layers", "swap_blocks", "transfer_blocks", "WritePlan", "_lib"]

@@ -56,6 +56,14 @@ SIGNATURES = {
     "lms_transfer_blocks": (c_int, [
         c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64, c_int32,
         c_void_p, c_int64, c_int64, c_int64, c_void_p]),
+    "lms_copy_blocks_host": (c_int, [
+        c_void_p, c_int64, c_int64, c_int64, c_int32, c_void_p, c_int64, c_int64, c_void_p]),
+    "lms_swap_blocks_host": (c_int, [
+        c_int, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64,
+        c_int32, c_int32, c_void_p, c_int64, c_int64, c_int64, c_void_p]),
+    "lms_transfer_blocks_host": (c_int, [
+        c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64, c_int32,
+        c_void_p, c_int64, c_int64, c_int64, c_void_p]),
     "lms_peer_enable": (c_int, [c_int]),
     "lms_host_alloc": (c_int, [c_int64, POINTER(c_void_p), POINTER(c_void_p)]),
     "lms_host_free": (c_int, [c_void_p]),

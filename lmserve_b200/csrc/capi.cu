@@ -19,6 +19,11 @@ constexpr int kMaxDevices = 64;
 struct DeviceState {
   int sms = 0;
   ErrRecord* err = nullptr;  // device memory, allocated on first use
+  // Device copy of the most recent host-side pair table (the *_host entry points).
+  long long* table = nullptr;
+  long long table_cap = 0;        // capacity in pairs
+  cudaEvent_t table_free = nullptr;  // recorded after the kernel that last read `table`
+  std::mutex table_mutex;
 };
 
 std::mutex g_mutex;
@@ -166,6 +171,53 @@ int chunk_copy(const void* src, int64_t src_layer, int64_t src_block, void* dst,
   LMS_CUDA(launch_chunk_copy(p, variant, policy, ctas, (cudaStream_t)stream));
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return LMS_OK;
+}
+
+// Uploads a host pair table into the device's table buffer on `stream` and returns the
+// device pointer.  The caller launches its kernel on `stream` and then calls table_release.
+int table_upload(DeviceState* ds, const int64_t* host_pairs, int64_t n_pairs,
+                 cudaStream_t stream, const long long** out) {
+  if (n_pairs > ds->table_cap) {
+    if (ds->table != nullptr) {
+      LMS_CUDA(cudaEventSynchronize(ds->table_free));
+      LMS_CUDA(cudaFree(ds->table));
+      ds->table = nullptr;
+      ds->table_cap = 0;
+    }
+    long long cap = 4096;
+    while (cap < n_pairs) cap *= 2;
+    LMS_CUDA(cudaMalloc(&ds->table, (size_t)cap * 16));
+    ds->table_cap = cap;
+    if (ds->table_free == nullptr)
+      LMS_CUDA(cudaEventCreateWithFlags(&ds->table_free, cudaEventDisableTiming));
+  } else if (ds->table_free != nullptr) {
+    LMS_CUDA(cudaStreamWaitEvent(stream, ds->table_free, 0));
+  }
+  LMS_CUDA(cudaMemcpyAsync(ds->table, host_pairs, (size_t)n_pairs * 16,
+                           cudaMemcpyHostToDevice, stream));
+  *out = ds->table;
+  return LMS_OK;
+}
+
+int table_release(DeviceState* ds, cudaStream_t stream) {
+  LMS_CUDA(cudaEventRecord(ds->table_free, stream));
+  return LMS_OK;
+}
+
+// Runs `launch(device_pairs)` with the host table uploaded first.
+template <class F>
+int with_host_table(const int64_t* host_pairs, int64_t n_pairs, void* stream, F launch) {
+  if (n_pairs < 0) return LMS_ERR_RANGE;
+  if (n_pairs == 0) return launch((const int64_t*)nullptr);
+  if (!host_pairs) return LMS_ERR_NULL;
+  DeviceState* ds = nullptr;
+  if (int rc = device_state(&ds)) return rc;
+  std::lock_guard<std::mutex> lock(ds->table_mutex);
+  const long long* dev_pairs = nullptr;
+  if (int rc = table_upload(ds, host_pairs, n_pairs, (cudaStream_t)stream, &dev_pairs)) return rc;
+  const int rc = launch((const int64_t*)dev_pairs);
+  const int rc2 = table_release(ds, (cudaStream_t)stream);
+  return rc != LMS_OK ? rc : rc2;
 }
 
 int sm_count() {
@@ -332,6 +384,46 @@ int lms_transfer_blocks(const void* src, int64_t src_layer_stride,
                     /*layer_major=*/1, kWhereTransfer,
                     tuned_variant(LMS_TUNE_XFER_VARIANT, 0), 0,
                     sm_count() * per_sm, stream);
+}
+
+int lms_copy_blocks_host(void* kv, int64_t layer_stride, int64_t block_stride,
+                         int64_t chunk_bytes, int32_t num_layers,
+                         const int64_t* host_pairs, int64_t n_pairs,
+                         int64_t num_blocks, void* stream) {
+  return with_host_table(host_pairs, n_pairs, stream, [&](const int64_t* pairs) {
+    return lms_copy_blocks(kv, layer_stride, block_stride, chunk_bytes, num_layers,
+                           pairs, n_pairs, num_blocks, stream);
+  });
+}
+
+int lms_swap_blocks_host(int direction, void* gpu, int64_t gpu_layer_stride,
+                         int64_t gpu_block_stride, void* host,
+                         int64_t host_block_stride, int64_t host_layer_stride,
+                         int64_t chunk_bytes, int32_t layer_begin, int32_t layer_end,
+                         const int64_t* host_pairs, int64_t n_pairs,
+                         int64_t num_gpu_blocks, int64_t num_host_blocks,
+                         void* stream) {
+  return with_host_table(host_pairs, n_pairs, stream, [&](const int64_t* pairs) {
+    return lms_swap_blocks(direction, gpu, gpu_layer_stride, gpu_block_stride, host,
+                           host_block_stride, host_layer_stride, chunk_bytes,
+                           layer_begin, layer_end, pairs, n_pairs, num_gpu_blocks,
+                           num_host_blocks, stream);
+  });
+}
+
+int lms_transfer_blocks_host(const void* src, int64_t src_layer_stride,
+                             int64_t src_block_stride, void* dst,
+                             int64_t dst_layer_stride, int64_t dst_block_stride,
+                             int64_t chunk_bytes, int32_t num_layers,
+                             const int64_t* host_pairs, int64_t n_pairs,
+                             int64_t num_src_blocks, int64_t num_dst_blocks,
+                             void* stream) {
+  return with_host_table(host_pairs, n_pairs, stream, [&](const int64_t* pairs) {
+    return lms_transfer_blocks(src, src_layer_stride, src_block_stride, dst,
+                               dst_layer_stride, dst_block_stride, chunk_bytes,
+                               num_layers, pairs, n_pairs, num_src_blocks,
+                               num_dst_blocks, stream);
+  });
 }
 
 int lms_peer_enable(int peer_device) {

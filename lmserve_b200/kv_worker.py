@@ -19,6 +19,7 @@ import numpy as np
 import torch
 
 from . import _lib
+from .disagg import build_push_pairs
 from .ops import cache_ops
 
 
@@ -264,17 +265,16 @@ class KVWorker:
         (after printing the reason) instead of raising, like the reference."""
         try:
             desc = CacheDescriptor.deserialize(remote_descs)
-            remote_ids = desc.block_ids[:len(block_ids)]
-            if len(remote_ids) != len(block_ids):
-                print("Creating transfer failed.")
+            try:
+                pairs = build_push_pairs(block_ids, desc.block_ids)
+            except ValueError as e:
+                print(f"Creating transfer failed. {e}")
                 return False
             with torch.cuda.device(self.device):
                 peer = self._peers.get(peer_name)
                 if peer is None:
                     peer = PeerCache(desc)
                     self._peers[peer_name] = peer
-                pairs = np.stack([np.asarray(block_ids, dtype=np.int64),
-                                  np.asarray(remote_ids, dtype=np.int64)], axis=1)
                 with torch.cuda.stream(stream or self.push_stream):
                     cache_ops.transfer_blocks(self.gpu_kv_caches, peer, pairs)
             return True

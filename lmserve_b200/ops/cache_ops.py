@@ -102,6 +102,16 @@ def _pairs_on_device(pairs, device: torch.device) -> torch.Tensor:
     return host.to(device, non_blocking=True)
 
 
+def _pair_table(pairs, device: torch.device):
+    """(on_device, keepalive, pointer, n): a device tensor is used in place; anything else is
+    flattened on the host and handed to the ``*_host`` entry points, which upload it."""
+    if isinstance(pairs, torch.Tensor) and pairs.is_cuda:
+        t = _pairs_on_device(pairs, device)
+        return True, t, t.data_ptr(), t.shape[0]
+    arr = flatten_block_map(pairs)
+    return False, arr, arr.ctypes.data, arr.shape[0]
+
+
 # --------------------------------------------------------------------- writes
 def fill_key_cache(
     key: torch.Tensor,
@@ -180,7 +190,9 @@ def reshape_and_cache_layers(
     _write_layers(key, value, kv_caches, slot_mapping)
 
 
-def _write_layers(key, value, kv_caches, slot_mapping) -> None:
+def _prepare_write(key, value, kv_caches, slot_mapping):
+    """Validates a multi-layer write and returns (device, keepalive, argument tuple without the
+    stream) for ``lms_reshape_and_cache_layers``."""
     for n, t in (("key", key), ("value", value), ("kv_caches", kv_caches)):
         _require_cuda(n, t)
     if key.dim() != 4 or value.dim() != 4 or key.shape != value.shape:
@@ -207,14 +219,48 @@ def _write_layers(key, value, kv_caches, slot_mapping) -> None:
     else:
         raise ValueError(f"slot_mapping must be [T] or [L, T], got {tuple(slots.shape)}")
     kbase = kv_caches.data_ptr()
-    with torch.cuda.device(dev):
-        _lib.check(_lib.lib().lms_reshape_and_cache_layers(
-            key.data_ptr(), value.data_ptr(), k_tok, v_tok,
+    args = (key.data_ptr(), value.data_ptr(), k_tok, v_tok,
             key.stride(0) * es, value.stride(0) * es,
             kbase, kbase + BS * row_bytes,
             kv_caches.stride(0) * es, kv_caches.stride(1) * es, row_bytes,
-            slots.data_ptr(), slot_layer, T, L, row_bytes, BS, NB * BS,
-            _stream_ptr(dev)))
+            slots.data_ptr(), slot_layer, T, L, row_bytes, BS, NB * BS)
+    return dev, (key, value, kv_caches, slots), args
+
+
+def _write_layers(key, value, kv_caches, slot_mapping) -> None:
+    dev, _keep, args = _prepare_write(key, value, kv_caches, slot_mapping)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().lms_reshape_and_cache_layers(*args, _stream_ptr(dev)))
+
+
+class WritePlan:
+    """A cache write whose arguments were validated and resolved once.
+
+    The decode loop writes the same ``key``/``value``/``slot_mapping`` buffers into the same
+    cache every step (the buffers are refilled in place), once per layer.  ``WritePlan`` does
+    the tensor checks and pointer arithmetic at construction; ``run()`` is one C call.  The
+    plan keeps the tensors alive and must be rebuilt if any of them is reallocated.
+
+    ``key``/``value`` may be ``[T, H, D]`` with ``kv_cache`` one layer ``[NB, 2, BS, H, D]``,
+    or ``[L, T, H, D]`` with the whole ``[L, NB, 2, BS, H, D]`` cache.
+    """
+
+    def __init__(self, key: torch.Tensor, value: torch.Tensor, kv_cache: torch.Tensor,
+                 slot_mapping: torch.Tensor):
+        if key.dim() == 3:
+            key, value, kv_cache = key.unsqueeze(0), value.unsqueeze(0), kv_cache.unsqueeze(0)
+        self.device, self._keep, self._args = _prepare_write(key, value, kv_cache, slot_mapping)
+        self._fn = _lib.lib().lms_reshape_and_cache_layers
+
+    def run(self, stream: Optional[int] = None) -> None:
+        """Enqueues the write on `stream` (a raw ``cudaStream_t`` value such as
+        ``torch.cuda.current_stream().cuda_stream``; default: the current stream).  The
+        current CUDA device must be the plan's device."""
+        if stream is None:
+            stream = torch.cuda.current_stream(self.device).cuda_stream
+        rc = self._fn(*self._args, stream)
+        if rc:
+            _lib.check(rc)
 
 
 # --------------------------------------------------------------------- copies
@@ -246,14 +292,14 @@ def copy_blocks(
     _require_cuda("kv_caches", kv_caches)
     dev = kv_caches.device
     L, NB, layer_stride, block_stride, chunk = _cache_geometry(kv_caches)
-    pairs = _pairs_on_device(src_to_dst, dev)
-    n = pairs.shape[0]
+    on_device, _keep, ptr, n = _pair_table(src_to_dst, dev)
     if n == 0:
         return
+    L_ = _lib.lib()
+    fn = L_.lms_copy_blocks if on_device else L_.lms_copy_blocks_host
     with torch.cuda.device(dev):
-        _lib.check(_lib.lib().lms_copy_blocks(
-            kv_caches.data_ptr(), layer_stride, block_stride, chunk, L,
-            pairs.data_ptr(), n, NB, _stream_ptr(dev)))
+        _lib.check(fn(kv_caches.data_ptr(), layer_stride, block_stride, chunk, L,
+                      ptr, n, NB, _stream_ptr(dev)))
 
 
 def swap_blocks(
@@ -283,16 +329,17 @@ def swap_blocks(
     l0, l1 = (0, L) if layers is None else layers
     if not (0 <= l0 <= l1 <= L):
         raise ValueError(f"layer range {layers} outside [0, {L}]")
-    pairs = _pairs_on_device(block_pairs, dev)
-    n = pairs.shape[0]
+    on_device, _keep, ptr, n = _pair_table(block_pairs, dev)
     if n == 0 or l0 == l1:
         return
+    L_ = _lib.lib()
+    fn = L_.lms_swap_blocks if on_device else L_.lms_swap_blocks_host
     with torch.cuda.device(dev):
-        _lib.check(_lib.lib().lms_swap_blocks(
+        _lib.check(fn(
             _lib.LMS_SWAP_OUT if direction == "out" else _lib.LMS_SWAP_IN,
             gpu_kv_caches.data_ptr(), layer_stride, block_stride,
             host_pool.device_ptr, host_pool.block_stride, host_pool.layer_stride,
-            chunk, l0, l1, pairs.data_ptr(), n, NB, host_pool.num_blocks,
+            chunk, l0, l1, ptr, n, NB, host_pool.num_blocks,
             _stream_ptr(dev)))
 
 
@@ -326,11 +373,11 @@ def transfer_blocks(
         dst_ptr = dst_kv_caches.device_ptr
     if dL != L or d_chunk != chunk:
         raise ValueError("source and destination caches must have the same layers and chunk size")
-    pairs = _pairs_on_device(block_pairs, dev)
-    n = pairs.shape[0]
+    on_device, _keep, ptr, n = _pair_table(block_pairs, dev)
     if n == 0:
         return
+    L_ = _lib.lib()
+    fn = L_.lms_transfer_blocks if on_device else L_.lms_transfer_blocks_host
     with torch.cuda.device(dev):
-        _lib.check(_lib.lib().lms_transfer_blocks(
-            src_kv_caches.data_ptr(), s_layer, s_block, dst_ptr, d_layer, d_block,
-            chunk, L, pairs.data_ptr(), n, NB, dNB, _stream_ptr(dev)))
+        _lib.check(fn(src_kv_caches.data_ptr(), s_layer, s_block, dst_ptr, d_layer, d_block,
+                      chunk, L, ptr, n, NB, dNB, _stream_ptr(dev)))

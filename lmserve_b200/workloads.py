@@ -277,13 +277,9 @@ def make_transfer(shape: KVShape, num_seqs: int, tokens_per_seq: int, seed: int,
 
 
 def transfer_peer(rank: int, world: int) -> Tuple[str, Optional[int]]:
-    """Role and partner of `rank` in the disaggregated pairing: prefill GPU g pushes to
-    decode GPU g + world/2 (rank i of one group talks to rank i of the other, as
-    ``runtime/src/llm_engine/worker.rs:502-515`` pairs them)."""
-    if world < 2 or world % 2:
-        return "none", None
-    half = world // 2
-    return ("prefill", rank + half) if rank < half else ("decode", rank - half)
+    """Role and partner of `rank` in the disaggregated pairing (see ``disagg.transfer_role``)."""
+    from .disagg import transfer_role
+    return transfer_role(rank, world)
 
 
 # ------------------------------------------------------------------ presets

@@ -147,7 +147,7 @@ def test_tp_sharded_decode_write_scaled(variant):
 def test_write_tile_sizes(variant, tile):
     set_variant(variant)
     _lib.lib().lms_set_tuning(_lib.TUNE_WRITE_TILE_BYTES, tile)
-    shape = W.SHAPES["llama31_8b"].scaled(num_layers=2, num_blocks=64)
+    shape = W.SHAPES["llama31_8b"].scaled(num_layers=2, num_blocks=640)
     w = W.make_decode_write(shape, 37, 8, 200, seed=36)
     run_layers_case(shape, w.slot_mapping, 46)
 
@@ -326,3 +326,74 @@ def test_runs_on_the_callers_stream():
         cache_ops.fill_key_cache(key, value, kc, vc, slots)
     s.synchronize()
     assert np.array_equal(to_words(kc), g["key_cache_out"])
+
+
+# ----------------------------------------------------------------- plans and pair tables
+def test_write_plan_matches_wrapper_and_tracks_buffer_refills():
+    shape = W.SHAPES["llama31_8b"].scaled(num_layers=3, num_blocks=256)
+    w = W.make_decode_write(shape, 24, 16, 150, seed=91)
+    rng = np.random.default_rng(92)
+    cache_words = W.normal_words(rng, shape.cache_shape, "bf16")
+    key = to_tensor(W.normal_words(rng, (3, 24, 8, 128), "bf16"), "bf16", DEV)
+    value = to_tensor(W.normal_words(rng, (3, 24, 8, 128), "bf16"), "bf16", DEV)
+    slots = torch.from_numpy(w.slot_mapping).to(DEV)
+    kv = to_tensor(cache_words, "bf16", DEV)
+    plan = cache_ops.WritePlan(key, value, kv, slots)
+    layer_plans = [cache_ops.WritePlan(key[l], value[l], kv[l], slots) for l in range(3)]
+    want = cache_words.copy()
+    for step in range(2):  # the second step refills the same buffers in place
+        if step:
+            key.copy_(to_tensor(W.normal_words(rng, (3, 24, 8, 128), "bf16"), "bf16", DEV))
+            slots.copy_(torch.from_numpy(np.roll(w.slot_mapping, 5)).to(DEV))
+        cache_oracle.reshape_and_cache_layers(to_words(key), to_words(value), want, slots.cpu().numpy())
+        plan.run()
+        torch.cuda.synchronize()
+        assert np.array_equal(to_words(kv), want)
+        kv.copy_(to_tensor(cache_words, "bf16", DEV))
+        for p in layer_plans:
+            p.run(torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+        assert np.array_equal(to_words(kv), want)
+        cache_words = want.copy()
+
+
+def test_pair_table_on_device_and_on_host_agree():
+    """Device tensors are read in place; host tables (dict, list, ndarray) are uploaded by the
+    library, including a table larger than its initial buffer and back-to-back calls on two
+    streams that share that buffer."""
+    L, NB, chunk_words = 2, 12000, 64
+    rng = np.random.default_rng(93)
+    words = rng.integers(0, 2**16, size=(L, NB, chunk_words), dtype=np.uint16)
+    perm = rng.permutation(NB)
+    pairs = np.stack([perm[:200].repeat(25), perm[200:5200]], axis=1).astype(np.int64)  # 5000 pairs
+    want = words.copy()
+    cache_oracle.copy_blocks(want, pairs)
+    for table in (pairs, torch.from_numpy(pairs).to(DEV), [tuple(p) for p in pairs.tolist()]):
+        kv = to_tensor(words, "fp16", DEV)
+        cache_ops.copy_blocks(kv, table)
+        torch.cuda.synchronize()
+        assert np.array_equal(to_words(kv), want)
+    # an unaligned slice of a device table is realigned by the wrapper
+    padded = torch.zeros(5001, 2, dtype=torch.int64, device=DEV)
+    padded[1:] = torch.from_numpy(pairs).to(DEV)
+    view = padded.view(-1)[1:-1].view(5000, 2)  # starts 8 bytes into the allocation
+    view.copy_(torch.from_numpy(pairs).to(DEV))
+    kv = to_tensor(words, "fp16", DEV)
+    cache_ops.copy_blocks(kv, view)
+    torch.cuda.synchronize()
+    assert np.array_equal(to_words(kv), want)
+    # two streams, different host tables, same library buffer
+    a, b = to_tensor(words, "fp16", DEV), to_tensor(words, "fp16", DEV)
+    torch.cuda.synchronize()
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    p1, p2 = pairs[:2500], pairs[2500:]
+    for _ in range(3):
+        with torch.cuda.stream(s1):
+            cache_ops.copy_blocks(a, p1)
+        with torch.cuda.stream(s2):
+            cache_ops.copy_blocks(b, p2)
+    torch.cuda.synchronize()
+    wa, wb = words.copy(), words.copy()
+    cache_oracle.copy_blocks(wa, p1)
+    cache_oracle.copy_blocks(wb, p2)
+    assert np.array_equal(to_words(a), wa) and np.array_equal(to_words(b), wb)
