@@ -123,9 +123,10 @@ int write_layers(const void* key, const void* value, int64_t key_tok,
   p.err = ds->err;
   p.checks = g_checks.load(std::memory_order_relaxed);
 
-  const int variant = tuned_variant(LMS_TUNE_WRITE_VARIANT, 0);
+  // 32-byte vectors where alignment allows (launch_write falls back to 16 bytes otherwise)
+  const int variant = tuned_variant(LMS_TUNE_WRITE_VARIANT, 1);
   const int tile = tuned(LMS_TUNE_WRITE_TILE_BYTES, 0);
-  LMS_CUDA(launch_write(p, variant, tile, (cudaStream_t)stream));
+  LMS_CUDA(launch_write(p, variant, tile, ds->sms, (cudaStream_t)stream));
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return LMS_OK;
 }
@@ -334,11 +335,11 @@ int lms_copy_blocks(void* kv, int64_t layer_stride, int64_t block_stride,
                     void* stream) {
   // Layer-major unit order: CTAs running at the same time work on one layer,
   // so a source block that fans out to many destinations is re-read from L2.
-  const int per_sm = tuned(LMS_TUNE_COPY_CTAS_PER_SM, 8);
+  const int per_sm = tuned(LMS_TUNE_COPY_CTAS_PER_SM, 2);
   return chunk_copy(kv, layer_stride, block_stride, kv, layer_stride,
                     block_stride, chunk_bytes, num_layers, pairs, n_pairs,
                     num_blocks, num_blocks, /*layer_major=*/1, kWhereCopyBlocks,
-                    tuned_variant(LMS_TUNE_COPY_VARIANT, 0), /*policy=*/1,
+                    tuned_variant(LMS_TUNE_COPY_VARIANT, 1), /*policy=*/1,
                     sm_count() * per_sm, stream);
 }
 

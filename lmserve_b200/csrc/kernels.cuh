@@ -48,7 +48,7 @@ struct WriteParams {
 
 // variant: 0 = 16-byte vectors, 1 = 32-byte vectors, 2 = bulk copies
 cudaError_t launch_write(const WriteParams& p, int variant, int tile_bytes,
-                         cudaStream_t stream);
+                         int sms, cudaStream_t stream);
 
 // ------------------------------------------------------------ chunk copies
 // One kernel family serves copy_blocks, swap-out, swap-in and transfer: every

@@ -7,10 +7,10 @@
 // per layer.
 //
 // Two implementations share one parameter block:
-//   * write_rows_vec  - a CTA owns a tile of tokens of one layer.  Slots are
-//     turned into destination byte offsets once, in shared memory; then every
-//     thread moves VPT 16- or 32-byte vectors with all loads issued before the
-//     first store, so a CTA keeps THREADS*VPT vectors in flight.
+//   * write_rows_vec  - a CTA owns a tile of tokens of one layer.  Slot loads and
+//     the first THREADS*VPT payload loads are issued together; the slots are
+//     then turned into destination byte offsets once, in shared memory, and
+//     every thread stores its 16- or 32-byte vectors.
 //   * write_rows_bulk - every lane of a warp owns one piece of a row and moves
 //     it with a bulk (TMA) copy global -> shared -> global; the warp shares one
 //     mbarrier.  Almost no instructions per byte.
@@ -41,6 +41,23 @@ __device__ __forceinline__ long long slot_offset(const WriteParams& p,
   return blk * p.block_stride + in * p.slot_stride;
 }
 
+// Splits vector index v of a tile into (token in tile, K|V, vector in row).
+template <bool POW2>
+__device__ __forceinline__ void split_vec(int v, int row_vecs, int row_shift,
+                                          int& ti, int& kv, int& c) {
+  if (POW2) {
+    ti = v >> (row_shift + 1);
+    kv = (v >> row_shift) & 1;
+    c = v & (row_vecs - 1);
+  } else {
+    const int vecs_per_tok = 2 * row_vecs;
+    ti = v / vecs_per_tok;
+    const int rem = v - ti * vecs_per_tok;
+    kv = rem >= row_vecs;
+    c = rem - kv * row_vecs;
+  }
+}
+
 template <class Vec, int THREADS, int VPT, bool POW2>
 __global__ void __launch_bounds__(THREADS)
 write_rows_vec(const WriteParams p, const int row_vecs, const int row_shift) {
@@ -51,21 +68,58 @@ write_rows_vec(const WriteParams p, const int row_vecs, const int row_shift) {
   const int t0 = tile * p.tok_tile;
   const int nt = min(p.tok_tile, p.num_tokens - t0);
 
-  const long long* slots = p.slots + (long long)layer * p.slot_layer + t0;
-  for (int i = threadIdx.x; i < nt; i += THREADS)
-    s_off[i] = slot_offset(p, slots[i], (long long)layer * p.slot_layer + t0 + i);
-  __syncthreads();
-
   const char* kin = p.key + (long long)layer * p.key_layer + (long long)t0 * p.key_tok;
   const char* vin = p.value + (long long)layer * p.val_layer + (long long)t0 * p.val_tok;
   char* kout = p.kcache + (long long)layer * p.cache_layer;
   char* vout = p.vcache + (long long)layer * p.cache_layer;
+  const int n_vec = nt * 2 * row_vecs;
 
-  const int vecs_per_tok = 2 * row_vecs;
-  const int n_vec = nt * vecs_per_tok;
+  // The source address of a row depends on the token only, the destination on its slot.
+  // So the first batch of payload loads is issued together with the slot loads, before the
+  // slots are known: one memory round trip instead of two in series.  (Rows of padded tokens
+  // are read and dropped.)
+  const long long* slots = p.slots + (long long)layer * p.slot_layer + t0;
+  long long my_slot[(kMaxTokTile + THREADS - 1) / THREADS];
+#pragma unroll
+  for (int k = 0; k < (kMaxTokTile + THREADS - 1) / THREADS; ++k) {
+    const int i = k * THREADS + threadIdx.x;
+    my_slot[k] = (i < nt) ? slots[i] : -1;
+  }
 
-  for (int base = 0; base < n_vec; base += THREADS * VPT) {
-    Vec r[VPT];
+  Vec r[VPT];
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int v = k * THREADS + threadIdx.x;
+    if (v < n_vec) {
+      int ti, kv, c;
+      split_vec<POW2>(v, row_vecs, row_shift, ti, kv, c);
+      const char* s = kv ? vin + (long long)ti * p.val_tok : kin + (long long)ti * p.key_tok;
+      ld(r[k], s + (long long)c * Vec::kBytes);
+    }
+  }
+
+#pragma unroll
+  for (int k = 0; k < (kMaxTokTile + THREADS - 1) / THREADS; ++k) {
+    const int i = k * THREADS + threadIdx.x;
+    if (i < nt)
+      s_off[i] = slot_offset(p, my_slot[k], (long long)layer * p.slot_layer + t0 + i);
+  }
+  __syncthreads();
+
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int v = k * THREADS + threadIdx.x;
+    if (v < n_vec) {
+      int ti, kv, c;
+      split_vec<POW2>(v, row_vecs, row_shift, ti, kv, c);
+      const long long off = s_off[ti];
+      if (off >= 0) st((kv ? vout : kout) + off + (long long)c * Vec::kBytes, r[k]);
+    }
+  }
+
+  // Tiles larger than one batch: the offsets are in shared memory now, padded rows are
+  // skipped before they are read.
+  for (int base = THREADS * VPT; base < n_vec; base += THREADS * VPT) {
     char* d[VPT];
 #pragma unroll
     for (int k = 0; k < VPT; ++k) {
@@ -73,20 +127,10 @@ write_rows_vec(const WriteParams p, const int row_vecs, const int row_shift) {
       d[k] = nullptr;
       if (v < n_vec) {
         int ti, kv, c;
-        if (POW2) {
-          ti = v >> (row_shift + 1);
-          kv = (v >> row_shift) & 1;
-          c = v & (row_vecs - 1);
-        } else {
-          ti = v / vecs_per_tok;
-          const int rem = v - ti * vecs_per_tok;
-          kv = rem >= row_vecs;
-          c = rem - kv * row_vecs;
-        }
+        split_vec<POW2>(v, row_vecs, row_shift, ti, kv, c);
         const long long off = s_off[ti];
         if (off >= 0) {
-          const char* s = kv ? vin + (long long)ti * p.val_tok
-                             : kin + (long long)ti * p.key_tok;
+          const char* s = kv ? vin + (long long)ti * p.val_tok : kin + (long long)ti * p.key_tok;
           ld(r[k], s + (long long)c * Vec::kBytes);
           d[k] = (kv ? vout : kout) + off + (long long)c * Vec::kBytes;
         }
@@ -176,13 +220,24 @@ inline int ilog2_exact(long long x) {
   return s;
 }
 
+// Tile choice: about two CTAs per SM for small launches (a decode step is tens of MiB, so
+// ramp-up and tail are a visible part of the run time and one wave is best), capped at
+// 128 KiB of payload per CTA for large ones.
+inline int auto_tile_bytes(const WriteParams& p, int sms) {
+  const long long total = (long long)p.num_layers * p.num_tokens * 2 * p.row_bytes;
+  const long long want = total / (2ll * sms);
+  int tile = 4096;
+  while (tile < 131072 && (long long)tile * 3 / 2 < want) tile *= 2;  // nearest power of two
+  return tile;
+}
+
 template <class Vec>
-cudaError_t launch_vec(WriteParams p, int tile_bytes, cudaStream_t stream) {
+cudaError_t launch_vec(WriteParams p, int tile_bytes, int sms, cudaStream_t stream) {
   constexpr int THREADS = 256;
   constexpr int VPT = 8;
   const int row_vecs = p.row_bytes / Vec::kBytes;
   const int row_shift = ilog2_exact(row_vecs);
-  if (tile_bytes <= 0) tile_bytes = THREADS * VPT * Vec::kBytes;
+  if (tile_bytes <= 0) tile_bytes = auto_tile_bytes(p, sms);
   int tok_tile = tile_bytes / (2 * p.row_bytes);
   tok_tile = tok_tile < 1 ? 1 : (tok_tile > kMaxTokTile ? kMaxTokTile : tok_tile);
   if (tok_tile > p.num_tokens) tok_tile = p.num_tokens;
@@ -202,7 +257,7 @@ cudaError_t launch_vec(WriteParams p, int tile_bytes, cudaStream_t stream) {
 }  // namespace
 
 cudaError_t launch_write(const WriteParams& p_in, int variant, int tile_bytes,
-                         cudaStream_t stream) {
+                         int sms, cudaStream_t stream) {
   WriteParams p = p_in;
   p.block_shift = ilog2_exact(p.block_size);
 
@@ -227,7 +282,7 @@ cudaError_t launch_write(const WriteParams& p_in, int variant, int tile_bytes,
         (long long)p.num_layers * p.num_tokens * 2 * p.pieces_per_row;
     constexpr int WARPS = 2;
     const size_t smem = (size_t)WARPS * 32 * piece;
-    int dev = 0, sms = 148;
+    int dev = 0;
     cudaGetDevice(&dev);
     static bool attr_set[64] = {};
     if (dev < 0 || dev >= 64 || !attr_set[dev]) {
@@ -239,15 +294,14 @@ cudaError_t launch_write(const WriteParams& p_in, int variant, int tile_bytes,
     }
     const long long tasks = (n_items + 31) / 32;
     long long ctas = (tasks + WARPS - 1) / WARPS;
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const long long resident = (long long)sms * ((200 * 1024) / (long long)(smem + 1024));
     if (ctas > resident) ctas = resident;
     if (ctas < 1) ctas = 1;
     write_rows_bulk<WARPS><<<(unsigned)ctas, WARPS * 32, smem, stream>>>(p, n_items);
     return cudaGetLastError();
   }
-  if (variant == 1) return launch_vec<V32>(p, tile_bytes, stream);
-  return launch_vec<V16>(p, tile_bytes, stream);
+  if (variant == 1) return launch_vec<V32>(p, tile_bytes, sms, stream);
+  return launch_vec<V16>(p, tile_bytes, sms, stream);
 }
 
 }  // namespace lms

@@ -127,9 +127,10 @@ def test_swap_round_trip_llama31_8b_full(pool):
     try:
         flat = kv.view(s.num_layers, s.num_blocks, -1)
         src = torch.from_numpy(w.out_pairs[:, 0].copy()).to(DEV)
+        base = torch.randn(1, flat.shape[2], device=DEV, dtype=torch.float32)
+        ramp = torch.arange(n_blocks, device=DEV, dtype=torch.float32)[:, None]
         for l in range(s.num_layers):
-            flat[l, src[:, None], :] = torch.randn(1, flat.shape[2], device=DEV, dtype=torch.bfloat16) \
-                + torch.arange(n_blocks, device=DEV, dtype=torch.bfloat16)[:, None] * 0.001 * (l + 1)
+            flat[l].index_copy_(0, src, (base + ramp * (0.001 * (l + 1))).to(torch.bfloat16))
         cache_ops.swap_blocks(kv, host, w.out_pairs, "out")
         cache_ops.swap_blocks(kv, host, w.in_pairs, "in")
         torch.cuda.synchronize()
