@@ -64,7 +64,8 @@ typedef enum lms_status {
 #define LMS_TUNE_SWAP_IN_CTAS 6  /* total CTAs of the host->GPU kernel */
 #define LMS_TUNE_XFER_CTAS_PER_SM 7
 #define LMS_TUNE_XFER_VARIANT 8  /* 0 = 16-byte ld/st, 1 = 32-byte, 2 = bulk-copy */
-#define LMS_TUNE__COUNT 9
+#define LMS_TUNE_WRITE_VPT 9     /* vectors per thread per pipeline batch of the cache write: 2, 4, 8 */
+#define LMS_TUNE__COUNT 10
 
 /* Library version (LMS_VERSION of the build). */
 int lms_version(void);
@@ -74,6 +75,14 @@ const char* lms_strerror(int status);
 
 /* Text of the last CUDA error seen by the calling thread inside this library. */
 const char* lms_last_cuda_error(void);
+
+/*
+ * Per-device set-up for the CURRENT device: queries the SM count and allocates the 32-byte
+ * device error record (cudaMalloc).  Every entry point does this on its first call on a
+ * device; call it explicitly first when that first call would otherwise fall inside a CUDA
+ * graph capture, where allocation is not permitted.  Idempotent.
+ */
+int lms_init_device(void);
 
 /* Overrides a launch tunable for every later call in this process. */
 int lms_set_tuning(int key, int value);

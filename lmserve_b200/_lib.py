@@ -31,12 +31,14 @@ TUNE_SWAP_OUT_CTAS = 5
 TUNE_SWAP_IN_CTAS = 6
 TUNE_XFER_CTAS_PER_SM = 7
 TUNE_XFER_VARIANT = 8
+TUNE_WRITE_VPT = 9
 
 # name -> (restype, argtypes); one entry per declaration in include/lmserve_kv.h
 SIGNATURES = {
     "lms_version": (c_int, []),
     "lms_strerror": (c_char_p, [c_int]),
     "lms_last_cuda_error": (c_char_p, []),
+    "lms_init_device": (c_int, []),
     "lms_set_tuning": (c_int, [c_int, c_int]),
     "lms_get_tuning": (c_int, [c_int]),
     "lms_set_debug_checks": (c_int, [c_int]),

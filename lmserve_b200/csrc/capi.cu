@@ -126,7 +126,8 @@ int write_layers(const void* key, const void* value, int64_t key_tok,
   // 32-byte vectors where alignment allows (launch_write falls back to 16 bytes otherwise)
   const int variant = tuned_variant(LMS_TUNE_WRITE_VARIANT, 1);
   const int tile = tuned(LMS_TUNE_WRITE_TILE_BYTES, 0);
-  LMS_CUDA(launch_write(p, variant, tile, ds->sms, (cudaStream_t)stream));
+  const int vpt = tuned(LMS_TUNE_WRITE_VPT, 2);
+  LMS_CUDA(launch_write(p, variant, tile, vpt, ds->sms, (cudaStream_t)stream));
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return LMS_OK;
 }
@@ -249,6 +250,11 @@ const char* lms_strerror(int status) {
 }
 
 const char* lms_last_cuda_error(void) { return g_cuda_msg; }
+
+int lms_init_device(void) {
+  DeviceState* ds = nullptr;
+  return device_state(&ds);
+}
 
 int lms_set_tuning(int key, int value) {
   if (key <= 0 || key >= LMS_TUNE__COUNT) return LMS_ERR_RANGE;

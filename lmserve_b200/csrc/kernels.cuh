@@ -46,9 +46,10 @@ struct WriteParams {
   int checks;
 };
 
-// variant: 0 = 16-byte vectors, 1 = 32-byte vectors, 2 = bulk copies
+// variant: 0 = 16-byte vectors, 1 = 32-byte vectors, 2 = bulk copies;
+// vpt: vectors per thread per pipeline batch (2, 4 or 8)
 cudaError_t launch_write(const WriteParams& p, int variant, int tile_bytes,
-                         int sms, cudaStream_t stream);
+                         int vpt, int sms, cudaStream_t stream);
 
 // ------------------------------------------------------------ chunk copies
 // One kernel family serves copy_blocks, swap-out, swap-in and transfer: every

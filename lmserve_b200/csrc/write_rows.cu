@@ -8,9 +8,10 @@
 //
 // Two implementations share one parameter block:
 //   * write_rows_vec  - a CTA owns a tile of tokens of one layer.  Slot loads and
-//     the first THREADS*VPT payload loads are issued together; the slots are
-//     then turned into destination byte offsets once, in shared memory, and
-//     every thread stores its 16- or 32-byte vectors.
+//     the first batch of payload loads are issued together; the slots are then
+//     turned into destination byte offsets once, in shared memory, and the tile
+//     is streamed as a two-stage software pipeline of 16- or 32-byte vectors
+//     (loads of batch b+1 in flight while batch b is stored).
 //   * write_rows_bulk - every lane of a warp owns one piece of a row and moves
 //     it with a bulk (TMA) copy global -> shared -> global; the warp shares one
 //     mbarrier.  Almost no instructions per byte.
@@ -73,72 +74,66 @@ write_rows_vec(const WriteParams p, const int row_vecs, const int row_shift) {
   char* kout = p.kcache + (long long)layer * p.cache_layer;
   char* vout = p.vcache + (long long)layer * p.cache_layer;
   const int n_vec = nt * 2 * row_vecs;
+  constexpr int kBatch = THREADS * VPT;
+  const int n_batches = (n_vec + kBatch - 1) / kBatch;
+
+  // Batch b of the tile: VPT vectors per thread, consecutive threads on consecutive vectors.
+  auto load_batch = [&](int b, Vec (&r)[VPT]) {
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      const int v = b * kBatch + k * THREADS + threadIdx.x;
+      if (v < n_vec) {
+        int ti, kv, c;
+        split_vec<POW2>(v, row_vecs, row_shift, ti, kv, c);
+        const char* s = kv ? vin + (long long)ti * p.val_tok : kin + (long long)ti * p.key_tok;
+        ld(r[k], s + (long long)c * Vec::kBytes);
+      }
+    }
+  };
+  auto store_batch = [&](int b, const Vec (&r)[VPT]) {
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      const int v = b * kBatch + k * THREADS + threadIdx.x;
+      if (v < n_vec) {
+        int ti, kv, c;
+        split_vec<POW2>(v, row_vecs, row_shift, ti, kv, c);
+        const long long off = s_off[ti];
+        if (off >= 0) st((kv ? vout : kout) + off + (long long)c * Vec::kBytes, r[k]);
+      }
+    }
+  };
 
   // The source address of a row depends on the token only, the destination on its slot.
-  // So the first batch of payload loads is issued together with the slot loads, before the
-  // slots are known: one memory round trip instead of two in series.  (Rows of padded tokens
-  // are read and dropped.)
+  // So the slot loads and the first batch of payload loads are issued together, before any
+  // slot is known: one memory round trip instead of two in series.  Rows of padded tokens
+  // are read and dropped.
   const long long* slots = p.slots + (long long)layer * p.slot_layer + t0;
-  long long my_slot[(kMaxTokTile + THREADS - 1) / THREADS];
+  constexpr int kSlotsPerThread = (kMaxTokTile + THREADS - 1) / THREADS;
+  long long my_slot[kSlotsPerThread];
 #pragma unroll
-  for (int k = 0; k < (kMaxTokTile + THREADS - 1) / THREADS; ++k) {
+  for (int k = 0; k < kSlotsPerThread; ++k) {
     const int i = k * THREADS + threadIdx.x;
     my_slot[k] = (i < nt) ? slots[i] : -1;
   }
 
-  Vec r[VPT];
-#pragma unroll
-  for (int k = 0; k < VPT; ++k) {
-    const int v = k * THREADS + threadIdx.x;
-    if (v < n_vec) {
-      int ti, kv, c;
-      split_vec<POW2>(v, row_vecs, row_shift, ti, kv, c);
-      const char* s = kv ? vin + (long long)ti * p.val_tok : kin + (long long)ti * p.key_tok;
-      ld(r[k], s + (long long)c * Vec::kBytes);
-    }
-  }
+  Vec ra[VPT], rb[VPT];
+  load_batch(0, ra);
 
 #pragma unroll
-  for (int k = 0; k < (kMaxTokTile + THREADS - 1) / THREADS; ++k) {
+  for (int k = 0; k < kSlotsPerThread; ++k) {
     const int i = k * THREADS + threadIdx.x;
     if (i < nt)
       s_off[i] = slot_offset(p, my_slot[k], (long long)layer * p.slot_layer + t0 + i);
   }
   __syncthreads();
 
-#pragma unroll
-  for (int k = 0; k < VPT; ++k) {
-    const int v = k * THREADS + threadIdx.x;
-    if (v < n_vec) {
-      int ti, kv, c;
-      split_vec<POW2>(v, row_vecs, row_shift, ti, kv, c);
-      const long long off = s_off[ti];
-      if (off >= 0) st((kv ? vout : kout) + off + (long long)c * Vec::kBytes, r[k]);
-    }
-  }
-
-  // Tiles larger than one batch: the offsets are in shared memory now, padded rows are
-  // skipped before they are read.
-  for (int base = THREADS * VPT; base < n_vec; base += THREADS * VPT) {
-    char* d[VPT];
-#pragma unroll
-    for (int k = 0; k < VPT; ++k) {
-      const int v = base + k * THREADS + threadIdx.x;
-      d[k] = nullptr;
-      if (v < n_vec) {
-        int ti, kv, c;
-        split_vec<POW2>(v, row_vecs, row_shift, ti, kv, c);
-        const long long off = s_off[ti];
-        if (off >= 0) {
-          const char* s = kv ? vin + (long long)ti * p.val_tok : kin + (long long)ti * p.key_tok;
-          ld(r[k], s + (long long)c * Vec::kBytes);
-          d[k] = (kv ? vout : kout) + off + (long long)c * Vec::kBytes;
-        }
-      }
-    }
-#pragma unroll
-    for (int k = 0; k < VPT; ++k)
-      if (d[k] != nullptr) st(d[k], r[k]);
+  // Software pipeline over the tile: the loads of batch b+1 are in flight while batch b is
+  // stored, so the memory system always has requests queued from this CTA.
+  for (int b = 0; b < n_batches; b += 2) {
+    if (b + 1 < n_batches) load_batch(b + 1, rb);
+    store_batch(b, ra);
+    if (b + 2 < n_batches) load_batch(b + 2, ra);
+    if (b + 1 < n_batches) store_batch(b + 1, rb);
   }
 }
 
@@ -220,21 +215,20 @@ inline int ilog2_exact(long long x) {
   return s;
 }
 
-// Tile choice: about two CTAs per SM for small launches (a decode step is tens of MiB, so
-// ramp-up and tail are a visible part of the run time and one wave is best), capped at
-// 128 KiB of payload per CTA for large ones.
+// Tile choice: about six CTAs per SM (five to eight are resident at 32-48 registers), so a
+// decode step - tens of MiB, where ramp-up and tail are a visible part of the run time - is
+// one wave of short CTAs; 4 KiB ... 64 KiB of payload per CTA.
 inline int auto_tile_bytes(const WriteParams& p, int sms) {
   const long long total = (long long)p.num_layers * p.num_tokens * 2 * p.row_bytes;
-  const long long want = total / (2ll * sms);
+  const long long want = total / (6ll * sms);
   int tile = 4096;
-  while (tile < 131072 && (long long)tile * 3 / 2 < want) tile *= 2;  // nearest power of two
+  while (tile < 65536 && (long long)tile * 3 / 2 < want) tile *= 2;  // nearest power of two
   return tile;
 }
 
-template <class Vec>
+template <class Vec, int VPT>
 cudaError_t launch_vec(WriteParams p, int tile_bytes, int sms, cudaStream_t stream) {
   constexpr int THREADS = 256;
-  constexpr int VPT = 8;
   const int row_vecs = p.row_bytes / Vec::kBytes;
   const int row_shift = ilog2_exact(row_vecs);
   if (tile_bytes <= 0) tile_bytes = auto_tile_bytes(p, sms);
@@ -254,10 +248,18 @@ cudaError_t launch_vec(WriteParams p, int tile_bytes, int sms, cudaStream_t stre
   return cudaGetLastError();
 }
 
+template <class Vec>
+cudaError_t launch_vec_vpt(const WriteParams& p, int tile_bytes, int vpt, int sms,
+                           cudaStream_t stream) {
+  if (vpt == 4) return launch_vec<Vec, 4>(p, tile_bytes, sms, stream);
+  if (vpt == 8) return launch_vec<Vec, 8>(p, tile_bytes, sms, stream);
+  return launch_vec<Vec, 2>(p, tile_bytes, sms, stream);
+}
+
 }  // namespace
 
 cudaError_t launch_write(const WriteParams& p_in, int variant, int tile_bytes,
-                         int sms, cudaStream_t stream) {
+                         int vpt, int sms, cudaStream_t stream) {
   WriteParams p = p_in;
   p.block_shift = ilog2_exact(p.block_size);
 
@@ -300,8 +302,8 @@ cudaError_t launch_write(const WriteParams& p_in, int variant, int tile_bytes,
     write_rows_bulk<WARPS><<<(unsigned)ctas, WARPS * 32, smem, stream>>>(p, n_items);
     return cudaGetLastError();
   }
-  if (variant == 1) return launch_vec<V32>(p, tile_bytes, sms, stream);
-  return launch_vec<V16>(p, tile_bytes, sms, stream);
+  if (variant == 1) return launch_vec_vpt<V32>(p, tile_bytes, vpt, sms, stream);
+  return launch_vec_vpt<V16>(p, tile_bytes, vpt, sms, stream);
 }
 
 }  // namespace lms

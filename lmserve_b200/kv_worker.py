@@ -178,6 +178,7 @@ class KVWorker:
         self.host_pool = (HostPool(num_host_blocks, self.num_layers, self.chunk_bytes)
                           if num_host_blocks > 0 else None)
         with torch.cuda.device(self.device):
+            _lib.check(_lib.lib().lms_init_device())
             self.dtoh_stream = torch.cuda.Stream()
             self.htod_stream = torch.cuda.Stream()
             self.push_stream = torch.cuda.Stream()

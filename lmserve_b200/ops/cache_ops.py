@@ -251,6 +251,9 @@ class WritePlan:
             key, value, kv_cache = key.unsqueeze(0), value.unsqueeze(0), kv_cache.unsqueeze(0)
         self.device, self._keep, self._args = _prepare_write(key, value, kv_cache, slot_mapping)
         self._fn = _lib.lib().lms_reshape_and_cache_layers
+        with torch.cuda.device(self.device):
+            # per-device set-up now, so that run() may be the first call inside a graph capture
+            _lib.check(_lib.lib().lms_init_device())
 
     def run(self, stream: Optional[int] = None) -> None:
         """Enqueues the write on `stream` (a raw ``cudaStream_t`` value such as

@@ -25,7 +25,7 @@ VARIANTS = [0, 1, 2]  # 16-byte vectors, 32-byte vectors, bulk (TMA) copies
 def _reset_tuning():
     yield
     L = _lib.lib()
-    for key in range(1, 9):
+    for key in range(1, 10):
         L.lms_set_tuning(key, -1)
     L.lms_set_debug_checks(0)
 
