@@ -48,7 +48,8 @@ typedef enum lms_status {
   LMS_ERR_CUDA = -4,      /* a CUDA runtime call failed (see lms_last_cuda_error) */
   LMS_ERR_INDEX = -5,     /* debug checks: an index was out of range         */
   LMS_ERR_PEER = -6,      /* peer access between the two devices unavailable */
-  LMS_ERR_UNSUPPORTED = -7
+  LMS_ERR_UNSUPPORTED = -7,
+  LMS_ERR_TOO_LARGE = -8  /* more pairs than a fixed-size table holds        */
 } lms_status;
 
 /* Direction of lms_swap_blocks. */
@@ -232,6 +233,34 @@ int lms_transfer_blocks_host(const void* src, int64_t src_layer_stride,
                              const int64_t* host_pairs, int64_t n_pairs,
                              int64_t num_src_blocks, int64_t num_dst_blocks,
                              void* stream);
+
+/*
+ * lms_copy_blocks_host for callers that must not allocate device memory.  (No counterpart in
+ * the reference; it exists because of how LMServe is deployed.)  An LMServe worker hands
+ * every byte the GPU has left to the KV cache when it starts (cache size = total * fraction -
+ * peak, runtime/src/llm_engine/engine.rs:56-90), so a cudaMalloc made later, in the middle of
+ * serving, can fail outright, and even when it succeeds it stalls every stream of the device
+ * while the driver services it.  lms_copy_blocks_host makes such a call whenever its device
+ * pair table has to be created or grown.  This variant never does: the uploaded (src, dst)
+ * table lives in a fixed array that is part of the library image itself - 256 KiB of device
+ * memory on every GPU that loads the library, held until the process exits - so it takes at
+ * most LMS_STATIC_MAX_PAIRS pairs and returns LMS_ERR_TOO_LARGE beyond that.  It calls no
+ * cudaMalloc / cudaFree, creates no event, and does not touch the per-device error record,
+ * therefore the debug index checks are not available through it.
+ *
+ * The first call on a device looks the array's device address up (once per device, with that
+ * device current); make that first call outside any stream capture.  All calls share the one
+ * array, and the array keeps whatever the previous call uploaded: only the first n_pairs
+ * entries are rewritten and only those are read, so stale entries are harmless, but two calls
+ * whose work overlaps on the GPU (different streams without a dependency between them) race
+ * on it - issue them on one stream or order them yourself.  `host_pairs` follows the rule of
+ * lms_copy_blocks_host (pageable memory may be reused on return).
+ */
+#define LMS_STATIC_MAX_PAIRS 16384
+int lms_copy_blocks_host_static(void* kv, int64_t layer_stride, int64_t block_stride,
+                                int64_t chunk_bytes, int32_t num_layers,
+                                const int64_t* host_pairs, int64_t n_pairs,
+                                void* stream);
 
 /* Enables peer access from the current device to `peer_device`
  * (LMS_ERR_PEER when the two GPUs cannot reach each other). */

@@ -19,6 +19,8 @@ LMS_ERR_CUDA = -4
 LMS_ERR_INDEX = -5
 LMS_ERR_PEER = -6
 LMS_ERR_UNSUPPORTED = -7
+LMS_ERR_TOO_LARGE = -8
+LMS_STATIC_MAX_PAIRS = 16384
 
 LMS_SWAP_OUT = 0
 LMS_SWAP_IN = 1
@@ -60,6 +62,8 @@ SIGNATURES = {
         c_void_p, c_int64, c_int64, c_int64, c_void_p]),
     "lms_copy_blocks_host": (c_int, [
         c_void_p, c_int64, c_int64, c_int64, c_int32, c_void_p, c_int64, c_int64, c_void_p]),
+    "lms_copy_blocks_host_static": (c_int, [
+        c_void_p, c_int64, c_int64, c_int64, c_int32, c_void_p, c_int64, c_void_p]),
     "lms_swap_blocks_host": (c_int, [
         c_int, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64,
         c_int32, c_int32, c_void_p, c_int64, c_int64, c_int64, c_void_p]),

@@ -222,6 +222,38 @@ int with_host_table(const int64_t* host_pairs, int64_t n_pairs, void* stream, F 
   return rc != LMS_OK ? rc : rc2;
 }
 
+// ---- fixed pair table of lms_copy_blocks_host_static -------------------------------------
+// Part of the library image: every device that loads the library holds these 256 KiB until
+// the process exits.  In host code the name below is only a handle for the runtime, not a
+// device address; static_table() asks the runtime for the address, per device.
+static __device__ __align__(256) long long g_static_pairs[2 * LMS_STATIC_MAX_PAIRS];
+
+struct StaticTable {
+  long long* table = nullptr;  // device address of g_static_pairs on this device
+  int sms = 0;
+};
+StaticTable g_static[kMaxDevices];
+std::mutex g_static_mutex;
+
+// Once per device, with that device current.  No allocation.
+int static_table(StaticTable** out) {
+  int dev = 0;
+  LMS_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return LMS_ERR_RANGE;
+  StaticTable& t = g_static[dev];
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  if (t.table == nullptr) {
+    void* ptr = nullptr;
+    LMS_CUDA(cudaGetSymbolAddress(&ptr, g_static_pairs));
+    int sms = 0;
+    LMS_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    t.sms = sms;
+    t.table = static_cast<long long*>(ptr);
+  }
+  *out = &t;
+  return LMS_OK;
+}
+
 int sm_count() {
   DeviceState* ds = nullptr;
   if (device_state(&ds) != LMS_OK) return 148;
@@ -245,6 +277,7 @@ const char* lms_strerror(int status) {
     case LMS_ERR_INDEX: return "a kernel met an out-of-range slot or block index";
     case LMS_ERR_PEER: return "peer access between the devices is unavailable";
     case LMS_ERR_UNSUPPORTED: return "unsupported";
+    case LMS_ERR_TOO_LARGE: return "more block pairs than the fixed-size table holds";
     default: return "unknown status";
   }
 }
@@ -401,6 +434,43 @@ int lms_copy_blocks_host(void* kv, int64_t layer_stride, int64_t block_stride,
     return lms_copy_blocks(kv, layer_stride, block_stride, chunk_bytes, num_layers,
                            pairs, n_pairs, num_blocks, stream);
   });
+}
+
+int lms_copy_blocks_host_static(void* kv, int64_t layer_stride, int64_t block_stride,
+                                int64_t chunk_bytes, int32_t num_layers,
+                                const int64_t* host_pairs, int64_t n_pairs,
+                                void* stream) {
+  if (n_pairs < 0 || num_layers < 0 || chunk_bytes <= 0 || chunk_bytes > (1ll << 30))
+    return LMS_ERR_RANGE;
+  if (n_pairs > LMS_STATIC_MAX_PAIRS) return LMS_ERR_TOO_LARGE;
+  if (n_pairs == 0 || num_layers == 0) return LMS_OK;
+  if (!kv || !host_pairs) return LMS_ERR_NULL;
+  if (!ptr16(kv) || !mult16(layer_stride) || !mult16(block_stride) || !mult16(chunk_bytes))
+    return LMS_ERR_ALIGN;
+
+  StaticTable* st = nullptr;
+  if (int rc = static_table(&st)) return rc;
+  // Upload into the fixed table, then the same kernel as lms_copy_blocks on the same stream.
+  LMS_CUDA(cudaMemcpyAsync(st->table, host_pairs, (size_t)n_pairs * 16,
+                           cudaMemcpyHostToDevice, (cudaStream_t)stream));
+  CopyParams p{};
+  p.src = (const char*)kv;
+  p.dst = (char*)kv;
+  p.src_layer = p.dst_layer = layer_stride;
+  p.src_block = p.dst_block = block_stride;
+  p.pairs = st->table;
+  p.n_pairs = n_pairs;
+  p.num_layers = num_layers;
+  p.layer_major = 1;
+  p.chunk_bytes = (int)chunk_bytes;
+  p.err = nullptr;  // no error record on this path
+  p.where = kWhereCopyBlocks;
+  p.checks = 0;
+  const int per_sm = tuned(LMS_TUNE_COPY_CTAS_PER_SM, 2);
+  LMS_CUDA(launch_chunk_copy(p, tuned_variant(LMS_TUNE_COPY_VARIANT, 1), /*policy=*/1,
+                             st->sms * per_sm, (cudaStream_t)stream));
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return LMS_OK;
 }
 
 int lms_swap_blocks_host(int direction, void* gpu, int64_t gpu_layer_stride,

@@ -305,6 +305,31 @@ def copy_blocks(
                       ptr, n, NB, _stream_ptr(dev)))
 
 
+def copy_blocks_no_alloc(
+    kv_caches: torch.Tensor,
+    src_to_dst: Union[Dict[int, List[int]], PairList],
+) -> None:
+    """``copy_blocks`` for a worker that must not allocate device memory while it serves.
+
+    Same arguments and result as :func:`copy_blocks` with a host-side table (dict, list or
+    ndarray), but the table is uploaded into a fixed 256 KiB array inside the library instead
+    of a buffer the library allocates on demand — see ``lms_copy_blocks_host_static`` in
+    ``include/lmserve_kv.h``.  At most ``LMS_STATIC_MAX_PAIRS`` (16 384) pairs per call;
+    consecutive calls must be on one stream or ordered by the caller, because they share the
+    array; debug index checks do not apply.
+    """
+    _require_cuda("kv_caches", kv_caches)
+    dev = kv_caches.device
+    L, NB, layer_stride, block_stride, chunk = _cache_geometry(kv_caches)
+    arr = flatten_block_map(src_to_dst)
+    if arr.shape[0] == 0:
+        return
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().lms_copy_blocks_host_static(
+            kv_caches.data_ptr(), layer_stride, block_stride, chunk, L,
+            arr.ctypes.data, arr.shape[0], _stream_ptr(dev)))
+
+
 def swap_blocks(
     gpu_kv_caches: torch.Tensor,
     host_pool,
