@@ -147,6 +147,57 @@ int lms_reshape_and_cache_layers(const void* key, const void* value,
                                  int64_t num_slots, void* stream);
 
 /*
+ * Planned write.  A decode loop issues the same write — same buffers, refilled in place —
+ * once per layer per step, and at 2 MiB per layer the host's argument marshalling costs more
+ * than the kernel.  lms_write_plan_create validates and stores the arguments of
+ * lms_reshape_and_cache_layers once; lms_write_plan_run enqueues the write on `stream` with
+ * the CUDA device the plan was created on current.  The plan holds no device memory and does
+ * not own any buffer; destroy it with lms_write_plan_destroy.  (The reference has no such
+ * object: it re-derives its launch arguments in Python on every call,
+ * runtime/worker/llm_worker/ops/cache_ops.py:46-59.)
+ */
+typedef struct lms_write_plan lms_write_plan;
+int lms_write_plan_create(const void* key, const void* value,
+                          int64_t key_token_stride, int64_t value_token_stride,
+                          int64_t key_layer_stride, int64_t value_layer_stride,
+                          void* key_cache, void* value_cache,
+                          int64_t cache_layer_stride,
+                          int64_t block_stride, int64_t slot_stride,
+                          const int64_t* slot_mapping, int64_t slot_layer_stride,
+                          int64_t num_tokens, int32_t num_layers,
+                          int64_t row_bytes, int32_t block_size,
+                          int64_t num_slots, lms_write_plan** plan);
+int lms_write_plan_run(const lms_write_plan* plan, void* stream);
+int lms_write_plan_destroy(lms_write_plan* plan);
+
+/*
+ * The same write addressed the way the reference's live call site addresses it —
+ *   flashinfer.append_paged_kv_cache(key, value, batch_indices, positions, kv_cache,
+ *                                    kv_indices, kv_indptr, kv_last_page_len)
+ *   runtime/worker/llm_worker/models/layers/attention.py:76-85
+ * (flashinfer-python, pinned 0.3.1.post1 by runtime/worker/uv.lock; kernel
+ * AppendPagedKVCacheKernel in its include/flashinfer/page.cuh) — so the index tensors that
+ * model_worker.py:399-433 already builds are used as they are, all int32 on the device:
+ *   page  = kv_indices[kv_indptr[batch_indices[t]] + positions[t] / block_size]
+ *   entry = positions[t] % block_size
+ *   key_cache  [page * block_stride + entry * slot_stride] <- key[t]   (value likewise)
+ * kv_last_page_len plays no part in the write and is not passed.  A negative batch index or
+ * position marks padding and is skipped.  num_layers > 1 writes all layers in one launch
+ * with the layer strides of lms_reshape_and_cache_layers; the per-layer call of the
+ * reference is num_layers = 1.  num_blocks: debug checks only (0 = unknown).
+ */
+int lms_append_paged_kv_cache(const void* key, const void* value,
+                              int64_t key_token_stride, int64_t value_token_stride,
+                              int64_t key_layer_stride, int64_t value_layer_stride,
+                              const int32_t* batch_indices, const int32_t* positions,
+                              void* key_cache, void* value_cache,
+                              int64_t cache_layer_stride, int64_t block_stride,
+                              int64_t slot_stride, const int32_t* kv_indices,
+                              const int32_t* kv_indptr, int64_t num_tokens,
+                              int32_t num_layers, int64_t row_bytes,
+                              int32_t block_size, int64_t num_blocks, void* stream);
+
+/*
  * Copy-on-write block copy — replaces
  *   copy_blocks               runtime/worker/llm_worker/ops/cache_ops.py:8-36
  *   copy_blocks_kernel        runtime/worker/llm_worker/ops/triton/cache_kernels.py:5-36

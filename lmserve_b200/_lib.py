@@ -52,6 +52,16 @@ SIGNATURES = {
         c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p,
         c_int64, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int32, c_int64,
         c_int32, c_int64, c_void_p]),
+    "lms_write_plan_create": (c_int, [
+        c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p,
+        c_int64, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int32, c_int64,
+        c_int32, c_int64, POINTER(c_void_p)]),
+    "lms_write_plan_run": (c_int, [c_void_p, c_void_p]),
+    "lms_write_plan_destroy": (c_int, [c_void_p]),
+    "lms_append_paged_kv_cache": (c_int, [
+        c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p,
+        c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_int64,
+        c_int32, c_int64, c_int32, c_int64, c_void_p]),
     "lms_copy_blocks": (c_int, [
         c_void_p, c_int64, c_int64, c_int64, c_int32, c_void_p, c_int64, c_int64, c_void_p]),
     "lms_swap_blocks": (c_int, [

@@ -4,11 +4,18 @@
 // entry point replaces are in include/lmserve_kv.h.
 #include <atomic>
 #include <mutex>
+#include <new>
 #include <stdio.h>
 #include <string.h>
 
 #include "../../include/lmserve_kv.h"
 #include "kernels.cuh"
+
+// A validated cache write (see lms_write_plan_create).
+struct lms_write_plan {
+  lms::WriteParams params;
+  bool empty;
+};
 
 namespace {
 
@@ -79,34 +86,62 @@ int tuned_variant(int key, int fallback) {
   return v > 0 ? v - 1 : fallback;
 }
 
-int write_layers(const void* key, const void* value, int64_t key_tok,
+// Page-table addressing of a write (all nullptr for direct slot addressing).
+struct PagedIndex {
+  const int32_t* batch_idx = nullptr;
+  const int32_t* positions = nullptr;
+  const int32_t* page_indices = nullptr;
+  const int32_t* page_indptr = nullptr;
+};
+
+// Validates the arguments of a write and fills the kernel parameter block (everything but
+// the per-launch fields: error record, checks flag).  LMS_OK with *empty = true means there
+// is nothing to do.
+int write_params(const void* key, const void* value, int64_t key_tok,
                  int64_t val_tok, int64_t key_layer, int64_t val_layer,
                  void* kcache, void* vcache, int64_t cache_layer,
                  int64_t block_stride, int64_t slot_stride,
                  const int64_t* slots, int64_t slot_layer, int64_t num_tokens,
                  int32_t num_layers, int64_t row_bytes, int32_t block_size,
-                 int64_t num_slots, void* stream) {
+                 int64_t num_slots, const PagedIndex* paged, WriteParams* out,
+                 bool* empty) {
+  *empty = false;
   if (num_tokens < 0 || num_layers < 0 || row_bytes <= 0 || block_size <= 0 ||
       num_tokens > 0x7fffffffll || row_bytes > (1 << 24) || slot_layer < 0 ||
       num_slots < 0)
     return LMS_ERR_RANGE;
-  if (num_tokens == 0 || num_layers == 0) return LMS_OK;
-  if (!key || !value || !kcache || !vcache || !slots) return LMS_ERR_NULL;
+  if (num_tokens == 0 || num_layers == 0) {
+    *empty = true;
+    return LMS_OK;
+  }
+  if (!key || !value || !kcache || !vcache) return LMS_ERR_NULL;
+  if (paged == nullptr) {
+    if (!slots) return LMS_ERR_NULL;
+  } else {
+    if (!paged->batch_idx || !paged->positions || !paged->page_indices || !paged->page_indptr)
+      return LMS_ERR_NULL;
+    if ((((uintptr_t)paged->batch_idx | (uintptr_t)paged->positions |
+          (uintptr_t)paged->page_indices | (uintptr_t)paged->page_indptr) & 3u) != 0)
+      return LMS_ERR_ALIGN;
+  }
   if (!ptr16(key) || !ptr16(value) || !ptr16(kcache) || !ptr16(vcache) ||
       ((uintptr_t)slots & 7u) != 0 || !mult16(key_tok) || !mult16(val_tok) ||
       !mult16(key_layer) || !mult16(val_layer) || !mult16(cache_layer) ||
       !mult16(block_stride) || !mult16(slot_stride) || !mult16(row_bytes))
     return LMS_ERR_ALIGN;
 
-  DeviceState* ds = nullptr;
-  if (int rc = device_state(&ds)) return rc;
-
   WriteParams p{};
   p.key = (const char*)key;
   p.value = (const char*)value;
   p.kcache = (char*)kcache;
   p.vcache = (char*)vcache;
-  p.slots = (const long long*)slots;
+  p.slots = paged ? nullptr : (const long long*)slots;
+  if (paged) {
+    p.batch_idx = paged->batch_idx;
+    p.positions = paged->positions;
+    p.page_indices = paged->page_indices;
+    p.page_indptr = paged->page_indptr;
+  }
   p.key_tok = key_tok;
   p.val_tok = val_tok;
   p.key_layer = key_layer;
@@ -120,9 +155,16 @@ int write_layers(const void* key, const void* value, int64_t key_tok,
   p.num_layers = num_layers;
   p.block_size = block_size;
   p.row_bytes = (int)row_bytes;
+  *out = p;
+  return LMS_OK;
+}
+
+// Launches a validated write on the current device.
+int write_launch(WriteParams p, void* stream) {
+  DeviceState* ds = nullptr;
+  if (int rc = device_state(&ds)) return rc;
   p.err = ds->err;
   p.checks = g_checks.load(std::memory_order_relaxed);
-
   // 32-byte vectors where alignment allows (launch_write falls back to 16 bytes otherwise)
   const int variant = tuned_variant(LMS_TUNE_WRITE_VARIANT, 1);
   const int tile = tuned(LMS_TUNE_WRITE_TILE_BYTES, 0);
@@ -130,6 +172,24 @@ int write_layers(const void* key, const void* value, int64_t key_tok,
   LMS_CUDA(launch_write(p, variant, tile, vpt, ds->sms, (cudaStream_t)stream));
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return LMS_OK;
+}
+
+int write_layers(const void* key, const void* value, int64_t key_tok,
+                 int64_t val_tok, int64_t key_layer, int64_t val_layer,
+                 void* kcache, void* vcache, int64_t cache_layer,
+                 int64_t block_stride, int64_t slot_stride,
+                 const int64_t* slots, int64_t slot_layer, int64_t num_tokens,
+                 int32_t num_layers, int64_t row_bytes, int32_t block_size,
+                 int64_t num_slots, void* stream, const PagedIndex* paged = nullptr) {
+  WriteParams p{};
+  bool empty = false;
+  if (int rc = write_params(key, value, key_tok, val_tok, key_layer, val_layer, kcache,
+                            vcache, cache_layer, block_stride, slot_stride, slots,
+                            slot_layer, num_tokens, num_layers, row_bytes, block_size,
+                            num_slots, paged, &p, &empty))
+    return rc;
+  if (empty) return LMS_OK;
+  return write_launch(p, stream);
 }
 
 // Shared validation + launch of the three chunk-copy entry points.
@@ -366,6 +426,71 @@ int lms_reshape_and_cache_layers(const void* key, const void* value,
                       value_cache, cache_layer_stride, block_stride,
                       slot_stride, slot_mapping, slot_layer_stride, num_tokens,
                       num_layers, row_bytes, block_size, num_slots, stream);
+}
+
+int lms_write_plan_create(const void* key, const void* value,
+                          int64_t key_token_stride, int64_t value_token_stride,
+                          int64_t key_layer_stride, int64_t value_layer_stride,
+                          void* key_cache, void* value_cache,
+                          int64_t cache_layer_stride,
+                          int64_t block_stride, int64_t slot_stride,
+                          const int64_t* slot_mapping, int64_t slot_layer_stride,
+                          int64_t num_tokens, int32_t num_layers,
+                          int64_t row_bytes, int32_t block_size,
+                          int64_t num_slots, lms_write_plan** plan) {
+  if (!plan) return LMS_ERR_NULL;
+  *plan = nullptr;
+  WriteParams p{};
+  bool empty = false;
+  if (int rc = write_params(key, value, key_token_stride, value_token_stride,
+                            key_layer_stride, value_layer_stride, key_cache, value_cache,
+                            cache_layer_stride, block_stride, slot_stride, slot_mapping,
+                            slot_layer_stride, num_tokens, num_layers, row_bytes,
+                            block_size, num_slots, nullptr, &p, &empty))
+    return rc;
+  // Per-device set-up now, so that the first run may already sit inside a graph capture.
+  DeviceState* ds = nullptr;
+  if (int rc = device_state(&ds)) return rc;
+  lms_write_plan* out = new (std::nothrow) lms_write_plan;
+  if (!out) return LMS_ERR_UNSUPPORTED;
+  out->params = p;
+  out->empty = empty;
+  *plan = out;
+  return LMS_OK;
+}
+
+int lms_write_plan_run(const lms_write_plan* plan, void* stream) {
+  if (!plan) return LMS_ERR_NULL;
+  if (plan->empty) return LMS_OK;
+  return write_launch(plan->params, stream);
+}
+
+int lms_write_plan_destroy(lms_write_plan* plan) {
+  delete plan;
+  return LMS_OK;
+}
+
+int lms_append_paged_kv_cache(const void* key, const void* value,
+                              int64_t key_token_stride, int64_t value_token_stride,
+                              int64_t key_layer_stride, int64_t value_layer_stride,
+                              const int32_t* batch_indices, const int32_t* positions,
+                              void* key_cache, void* value_cache,
+                              int64_t cache_layer_stride, int64_t block_stride,
+                              int64_t slot_stride, const int32_t* kv_indices,
+                              const int32_t* kv_indptr, int64_t num_tokens,
+                              int32_t num_layers, int64_t row_bytes,
+                              int32_t block_size, int64_t num_blocks, void* stream) {
+  if (num_blocks < 0 || num_blocks > (1ll << 40)) return LMS_ERR_RANGE;
+  PagedIndex paged;
+  paged.batch_idx = batch_indices;
+  paged.positions = positions;
+  paged.page_indices = kv_indices;
+  paged.page_indptr = kv_indptr;
+  return write_layers(key, value, key_token_stride, value_token_stride,
+                      key_layer_stride, value_layer_stride, key_cache, value_cache,
+                      cache_layer_stride, block_stride, slot_stride, nullptr, 0,
+                      num_tokens, num_layers, row_bytes, block_size,
+                      num_blocks * (int64_t)block_size, stream, &paged);
 }
 
 int lms_copy_blocks(void* kv, int64_t layer_stride, int64_t block_stride,

@@ -25,7 +25,13 @@ struct WriteParams {
   const char* value;
   char* kcache;
   char* vcache;
-  const long long* slots;
+  const long long* slots;          // direct addressing: slot per token (nullptr in paged mode)
+  // Paged addressing (slots == nullptr): token t belongs to request batch_idx[t] at position
+  // positions[t]; its slot is page_indices[page_indptr[b] + pos / BS] * BS + pos % BS.
+  const int* batch_idx;
+  const int* positions;
+  const int* page_indices;
+  const int* page_indptr;
   long long key_tok, val_tok;      // bytes between consecutive tokens
   long long key_layer, val_layer;  // bytes between consecutive layers (inputs)
   long long cache_layer;           // bytes between consecutive layers (cache)

@@ -59,6 +59,39 @@ __device__ __forceinline__ void split_vec(int v, int row_vecs, int row_shift,
   }
 }
 
+// Slot of token t (index into the call's token list) of `layer`, fetched in two steps so
+// that the independent loads of step one can be issued before the payload loads and the
+// dependent page-table walk of step two after them.
+struct SlotRaw {
+  long long a;  // direct: the slot;  paged: batch index
+  int b;        // paged: position
+};
+__device__ __forceinline__ SlotRaw slot_fetch_begin(const WriteParams& p, int layer, int t) {
+  SlotRaw r;
+  r.b = 0;
+  if (p.slots != nullptr) {
+    r.a = p.slots[(long long)layer * p.slot_layer + t];
+  } else {
+    r.a = p.batch_idx[t];
+    r.b = p.positions[t];
+  }
+  return r;
+}
+__device__ __forceinline__ long long slot_fetch_end(const WriteParams& p, const SlotRaw& r) {
+  if (p.slots != nullptr) return r.a;
+  if (r.a < 0 || r.b < 0) return -1;  // padding: negative batch index or position
+  int pg, in;
+  if (p.block_shift >= 0) {
+    pg = r.b >> p.block_shift;
+    in = r.b & ((1 << p.block_shift) - 1);
+  } else {
+    pg = r.b / p.block_size;
+    in = r.b - pg * p.block_size;
+  }
+  const long long page = p.page_indices[p.page_indptr[r.a] + pg];
+  return page * p.block_size + in;
+}
+
 template <class Vec, int THREADS, int VPT, bool POW2>
 __global__ void __launch_bounds__(THREADS)
 write_rows_vec(const WriteParams p, const int row_vecs, const int row_shift) {
@@ -107,13 +140,12 @@ write_rows_vec(const WriteParams p, const int row_vecs, const int row_shift) {
   // So the slot loads and the first batch of payload loads are issued together, before any
   // slot is known: one memory round trip instead of two in series.  Rows of padded tokens
   // are read and dropped.
-  const long long* slots = p.slots + (long long)layer * p.slot_layer + t0;
   constexpr int kSlotsPerThread = (kMaxTokTile + THREADS - 1) / THREADS;
-  long long my_slot[kSlotsPerThread];
+  SlotRaw my_slot[kSlotsPerThread];
 #pragma unroll
   for (int k = 0; k < kSlotsPerThread; ++k) {
     const int i = k * THREADS + threadIdx.x;
-    my_slot[k] = (i < nt) ? slots[i] : -1;
+    if (i < nt) my_slot[k] = slot_fetch_begin(p, layer, t0 + i);
   }
 
   Vec ra[VPT], rb[VPT];
@@ -123,7 +155,8 @@ write_rows_vec(const WriteParams p, const int row_vecs, const int row_shift) {
   for (int k = 0; k < kSlotsPerThread; ++k) {
     const int i = k * THREADS + threadIdx.x;
     if (i < nt)
-      s_off[i] = slot_offset(p, my_slot[k], (long long)layer * p.slot_layer + t0 + i);
+      s_off[i] = slot_offset(p, slot_fetch_end(p, my_slot[k]),
+                             (long long)layer * p.slot_layer + t0 + i);
   }
   __syncthreads();
 
@@ -174,7 +207,8 @@ write_rows_bulk(const WriteParams p, const long long n_items) {
       const int t = (int)(q % p.num_tokens);
       const int layer = (int)(q / p.num_tokens);
       const long long si = (long long)layer * p.slot_layer + t;
-      const long long off = slot_offset(p, p.slots[si], si);
+      const long long off =
+          slot_offset(p, slot_fetch_end(p, slot_fetch_begin(p, layer, t)), si);
       if (off >= 0) {
         const long long po = (long long)piece * p.piece_bytes;
         src = (kv ? p.value + (long long)layer * p.val_layer + (long long)t * p.val_tok

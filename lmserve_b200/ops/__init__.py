@@ -1,8 +1,8 @@
 """Host-side mirror of LMServe's ``llm_worker.ops`` cache operators."""
-from .cache_ops import (copy_blocks, copy_blocks_no_alloc, fill_key_cache, reshape_and_cache,
+from .cache_ops import (append_paged_kv_cache, copy_blocks, copy_blocks_no_alloc, fill_key_cache, reshape_and_cache,
                         reshape_and_cache_layers, swap_blocks, transfer_blocks,
                         flatten_block_map, WritePlan)
 
-__all__ = ["copy_blocks", "copy_blocks_no_alloc", "fill_key_cache", "reshape_and_cache",
+__all__ = ["append_paged_kv_cache", "copy_blocks", "copy_blocks_no_alloc", "fill_key_cache", "reshape_and_cache",
            "reshape_and_cache_layers", "swap_blocks", "transfer_blocks",
            "flatten_block_map", "WritePlan"]

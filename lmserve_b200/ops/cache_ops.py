@@ -16,6 +16,7 @@ CUDA device are rejected, and a missing shared library is an ImportError.
 """
 from __future__ import annotations
 
+import ctypes
 from typing import Dict, Iterable, List, Optional, Sequence, Tuple, Union
 
 import numpy as np
@@ -190,6 +191,81 @@ def reshape_and_cache_layers(
     _write_layers(key, value, kv_caches, slot_mapping)
 
 
+def append_paged_kv_cache(
+    append_key: torch.Tensor,
+    append_value: torch.Tensor,
+    batch_indices: torch.Tensor,
+    positions: torch.Tensor,
+    paged_kv_cache,
+    kv_indices: torch.Tensor,
+    kv_indptr: torch.Tensor,
+    kv_last_page_len: Optional[torch.Tensor] = None,
+    kv_layout: str = "NHD",
+) -> None:
+    """Drop-in for ``flashinfer.append_paged_kv_cache`` as LMServe calls it
+    (``models/layers/attention.py:76-85``): same argument order and meaning, same in-place
+    result, so the call site changes only its import.
+
+    ``append_key``/``append_value``: ``[T, H, D]``; ``batch_indices``/``positions``: int32
+    ``[T]`` (request index and position of every appended token, as produced by
+    ``flashinfer.get_batch_indices_positions`` at ``model_worker.py:425-433``);
+    ``paged_kv_cache``: one layer's ``[num_pages, 2, page_size, H, D]`` tensor, or a
+    ``(k_cache, v_cache)`` pair of ``[num_pages, page_size, H, D]`` tensors; ``kv_indices`` /
+    ``kv_indptr``: int32 page table in CSR form.  ``kv_last_page_len`` is accepted and ignored
+    (the write does not need it).  Only the ``"NHD"`` layout, the one LMServe uses.
+    """
+    if kv_layout != "NHD":
+        raise ValueError("only the NHD layout (LMServe's) is supported")
+    _require_cuda("append_key", append_key)
+    _require_cuda("append_value", append_value)
+    if isinstance(paged_kv_cache, (tuple, list)):
+        k_cache, v_cache = paged_kv_cache
+        _require_cuda("k_cache", k_cache)
+        _require_cuda("v_cache", v_cache)
+        if k_cache.dim() != 4 or k_cache.shape != v_cache.shape or k_cache.stride() != v_cache.stride():
+            raise ValueError("k_cache and v_cache must both be [num_pages, page_size, H, D]")
+        NB, BS, H, D = k_cache.shape
+        block_stride = k_cache.stride(0) * k_cache.element_size()
+        page_ok = NB == 0 or k_cache[0].is_contiguous()
+        kptr, vptr, cdtype, dev = k_cache.data_ptr(), v_cache.data_ptr(), k_cache.dtype, k_cache.device
+    else:
+        _require_cuda("paged_kv_cache", paged_kv_cache)
+        if paged_kv_cache.dim() != 5 or paged_kv_cache.shape[1] != 2:
+            raise ValueError("paged_kv_cache must be [num_pages, 2, page_size, H, D]")
+        NB, _, BS, H, D = paged_kv_cache.shape
+        block_stride = paged_kv_cache.stride(0) * paged_kv_cache.element_size()
+        page_ok = NB == 0 or paged_kv_cache[0].is_contiguous()
+        kptr = paged_kv_cache.data_ptr()
+        vptr = kptr + BS * H * D * paged_kv_cache.element_size()
+        cdtype, dev = paged_kv_cache.dtype, paged_kv_cache.device
+    if not page_ok:
+        raise ValueError("each cache page must be contiguous")
+    k_tok, row_bytes = _row_layout("append_key", append_key)
+    v_tok, v_row = _row_layout("append_value", append_value)
+    T = append_key.shape[0]
+    if tuple(append_key.shape[1:]) != (H, D) or append_value.shape != append_key.shape:
+        raise ValueError("append_key / append_value do not match the cache's [H, D]")
+    if append_key.dtype != cdtype or append_value.dtype != cdtype:
+        raise TypeError("cache dtype must match key/value dtype (bytes are copied, not converted)")
+    idx = []
+    for name, t in (("batch_indices", batch_indices), ("positions", positions),
+                    ("kv_indices", kv_indices), ("kv_indptr", kv_indptr)):
+        _require_cuda(name, t)
+        if t.dtype != torch.int32:
+            raise TypeError(f"{name} must be int32 (got {t.dtype})")
+        idx.append(t.contiguous())
+    if idx[0].numel() != T or idx[1].numel() != T:
+        raise ValueError("batch_indices and positions need one entry per appended token")
+    if T == 0:
+        return
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().lms_append_paged_kv_cache(
+            append_key.data_ptr(), append_value.data_ptr(), k_tok, v_tok, 0, 0,
+            idx[0].data_ptr(), idx[1].data_ptr(), kptr, vptr, 0, block_stride, row_bytes,
+            idx[2].data_ptr(), idx[3].data_ptr(), T, 1, row_bytes, BS, NB,
+            _stream_ptr(dev)))
+
+
 def _prepare_write(key, value, kv_caches, slot_mapping):
     """Validates a multi-layer write and returns (device, keepalive, argument tuple without the
     stream) for ``lms_reshape_and_cache_layers``."""
@@ -249,11 +325,15 @@ class WritePlan:
                  slot_mapping: torch.Tensor):
         if key.dim() == 3:
             key, value, kv_cache = key.unsqueeze(0), value.unsqueeze(0), kv_cache.unsqueeze(0)
-        self.device, self._keep, self._args = _prepare_write(key, value, kv_cache, slot_mapping)
-        self._fn = _lib.lib().lms_reshape_and_cache_layers
+        self.device, self._keep, args = _prepare_write(key, value, kv_cache, slot_mapping)
+        handle = ctypes.c_void_p()
         with torch.cuda.device(self.device):
-            # per-device set-up now, so that run() may be the first call inside a graph capture
-            _lib.check(_lib.lib().lms_init_device())
+            # validates once and does the per-device set-up, so that run() may be the first
+            # call inside a graph capture
+            _lib.check(_lib.lib().lms_write_plan_create(*args, ctypes.byref(handle)))
+        self._handle = handle
+        self._run = _lib.lib().lms_write_plan_run
+        self._destroy = _lib.lib().lms_write_plan_destroy
 
     def run(self, stream: Optional[int] = None) -> None:
         """Enqueues the write on `stream` (a raw ``cudaStream_t`` value such as
@@ -261,9 +341,15 @@ class WritePlan:
         current CUDA device must be the plan's device."""
         if stream is None:
             stream = torch.cuda.current_stream(self.device).cuda_stream
-        rc = self._fn(*self._args, stream)
+        rc = self._run(self._handle, stream)
         if rc:
             _lib.check(rc)
+
+    def __del__(self):
+        h = getattr(self, "_handle", None)
+        if h:
+            self._destroy(h)
+            self._handle = None
 
 
 # --------------------------------------------------------------------- copies

@@ -151,6 +151,15 @@ def make_decode_write(shape: KVShape, batch: int, ctx_lo: int, ctx_hi: int, seed
     return DecodeWrite(shape, ctx, slots, bt)
 
 
+def paged_metadata(tables: List[np.ndarray]):
+    """CSR page table (kv_indptr, kv_indices), int32, of a list of per-sequence block tables —
+    the arrays ``model_worker.py:399-423`` builds from ``InferInput.block_ids``."""
+    counts = np.array([len(t) for t in tables], dtype=np.int64)
+    indptr = np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)
+    indices = (np.concatenate(tables) if tables else np.empty(0, np.int64)).astype(np.int32)
+    return indptr, indices
+
+
 @dataclass
 class PrefillChunkCow:
     """Chunked prefill (runs of consecutive slots) plus copy-on-write pairs."""

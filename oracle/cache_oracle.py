@@ -73,6 +73,34 @@ def reshape_and_cache(key: np.ndarray, value: np.ndarray, kv_cache: np.ndarray,
         c[slot // BS, 1, slot % BS, :] = v[t]
 
 
+def append_paged_kv_cache(append_key: np.ndarray, append_value: np.ndarray,
+                          batch_indices: np.ndarray, positions: np.ndarray,
+                          kv_cache: np.ndarray, kv_indices: np.ndarray,
+                          kv_indptr: np.ndarray) -> None:
+    """The live cache write of the reference, ``flashinfer.append_paged_kv_cache`` as called at
+    ``models/layers/attention.py:76-85``.  flashinfer is a third-party dependency that is not
+    part of the LMServe tree (``flashinfer-python`` 0.3.1.post1 in ``runtime/worker/uv.lock``);
+    this restates its published algorithm (``AppendPagedKVCacheKernel``,
+    ``include/flashinfer/page.cuh``): for appended row ``i``,
+    ``page = indices[indptr[batch_indices[i]] + positions[i] // page_size]``,
+    ``entry = positions[i] % page_size``, K row to ``cache[page, 0, entry]``, V row to
+    ``cache[page, 1, entry]`` (NHD layout).  kv_cache: [num_pages, 2, page_size, H, D]."""
+    NB, two, BS = kv_cache.shape[:3]
+    assert two == 2
+    T = append_key.shape[0]
+    row = int(np.prod(append_key.shape[1:]))
+    c = kv_cache.reshape(NB, 2, BS, row)
+    k = append_key.reshape(T, row)
+    v = append_value.reshape(T, row)
+    for i in range(T):
+        b, pos = int(batch_indices[i]), int(positions[i])
+        if b < 0 or pos < 0:
+            continue
+        page = int(kv_indices[int(kv_indptr[b]) + pos // BS])
+        c[page, 0, pos % BS, :] = k[i]
+        c[page, 1, pos % BS, :] = v[i]
+
+
 def reshape_and_cache_layers(key: np.ndarray, value: np.ndarray, kv_caches: np.ndarray,
                              slot_mapping: np.ndarray) -> None:
     """Per-layer loop of ``models/llama.py:236-242``: layer ``l`` writes ``key[l]`` into

@@ -397,3 +397,68 @@ def test_pair_table_on_device_and_on_host_agree():
     cache_oracle.copy_blocks(wa, p1)
     cache_oracle.copy_blocks(wb, p2)
     assert np.array_equal(to_words(a), wa) and np.array_equal(to_words(b), wb)
+
+
+# ----------------------------------------------------------------- flashinfer-style call
+def paged_case(seed, num_seqs, chunk, num_blocks=400, H=4, D=64):
+    shape = W.KVShape("paged", 1, H, D, "bf16", num_blocks)
+    w = W.make_prefill_cow(shape, num_seqs, chunk, 300, 0, 0, seed=seed)
+    indptr, indices = W.paged_metadata(w.tables.tables)
+    T = len(w.slot_mapping)
+    batch = np.repeat(np.arange(num_seqs, dtype=np.int32), chunk)
+    pos = np.empty(T, np.int32)
+    for i, s in enumerate(w.slot_mapping):
+        t = w.tables.tables[batch[i]]
+        pos[i] = int(np.nonzero(t == s // 16)[0][0]) * 16 + s % 16
+    rng = np.random.default_rng(seed + 1)
+    key, value = W.normal_words(rng, (T, H, D), "bf16"), W.normal_words(rng, (T, H, D), "bf16")
+    cache = W.normal_words(rng, shape.cache_shape[1:], "bf16")
+    return shape, key, value, cache, batch, pos, indices, indptr
+
+
+@pytest.mark.parametrize("variant", VARIANTS)
+def test_append_paged_kv_cache_vs_oracle(variant):
+    set_variant(variant)
+    shape, key, value, cache, batch, pos, indices, indptr = paged_case(101, 7, 33)
+    batch[[4, 90]] = -1                       # padded rows are skipped
+    want = cache.copy()
+    cache_oracle.append_paged_kv_cache(key, value, batch, pos, want, indices, indptr)
+    got = to_tensor(cache, "bf16", DEV)
+    dev = lambda a: torch.from_numpy(a).to(DEV)
+    cache_ops.append_paged_kv_cache(to_tensor(key, "bf16", DEV), to_tensor(value, "bf16", DEV),
+                                    dev(batch), dev(pos), got, dev(indices), dev(indptr),
+                                    torch.ones(7, dtype=torch.int32, device=DEV))
+    torch.cuda.synchronize()
+    assert np.array_equal(to_words(got), want)
+    # separate K and V caches, as flashinfer also accepts
+    kc = to_tensor(np.ascontiguousarray(cache[:, 0]), "bf16", DEV)
+    vc = to_tensor(np.ascontiguousarray(cache[:, 1]), "bf16", DEV)
+    cache_ops.append_paged_kv_cache(to_tensor(key, "bf16", DEV), to_tensor(value, "bf16", DEV),
+                                    dev(batch), dev(pos), (kc, vc), dev(indices), dev(indptr), None)
+    torch.cuda.synchronize()
+    assert np.array_equal(to_words(kc), want[:, 0]) and np.array_equal(to_words(vc), want[:, 1])
+    with pytest.raises(TypeError, match="int32"):
+        cache_ops.append_paged_kv_cache(to_tensor(key, "bf16", DEV), to_tensor(value, "bf16", DEV),
+                                        dev(batch).long(), dev(pos), got, dev(indices), dev(indptr))
+
+
+def test_append_paged_kv_cache_matches_flashinfer():
+    """The reference's live cache write is flashinfer's kernel; where flashinfer is importable on
+    the GPU box, its result on the same inputs is the golden output."""
+    flashinfer = pytest.importorskip("flashinfer")
+    shape, key, value, cache, batch, pos, indices, indptr = paged_case(103, 9, 50, H=8, D=128)
+    dev = lambda a: torch.from_numpy(a).to(DEV)
+    k, v = to_tensor(key, "bf16", DEV), to_tensor(value, "bf16", DEV)
+    last = torch.ones(9, dtype=torch.int32, device=DEV)
+    theirs = to_tensor(cache, "bf16", DEV)
+    try:
+        flashinfer.append_paged_kv_cache(k, v, dev(batch), dev(pos), theirs, dev(indices),
+                                         dev(indptr), last)
+        torch.cuda.synchronize()
+    except Exception as e:  # JIT toolchain missing on the box, etc.
+        pytest.skip(f"flashinfer could not run here: {e!r}"[:200])
+    ours = to_tensor(cache, "bf16", DEV)
+    cache_ops.append_paged_kv_cache(k, v, dev(batch), dev(pos), ours, dev(indices), dev(indptr), last)
+    torch.cuda.synchronize()
+    assert torch.equal(ours.view(torch.int16), theirs.view(torch.int16))
+    assert not np.array_equal(to_words(ours), cache)

@@ -157,3 +157,33 @@ def test_golden_regenerates_from_reference(tmp_path):
     out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300)
     assert out.returncode == 0, out.stderr[-2000:]
     assert out.stdout.strip().splitlines()[-1] == load_json("plumbing_llama32_1b")["outputs"]["kv_caches"]
+
+
+def test_paged_append_equals_slot_write():
+    """flashinfer's (batch index, position, page table) addressing and the slot mapping
+    ``table[pos // BS] * BS + pos % BS`` describe the same write."""
+    shape = W.SHAPES["llama31_8b"].scaled(num_layers=1, num_blocks=96, num_kv_heads=2, head_dim=16)
+    w = W.make_prefill_cow(shape, 5, 40, 200, 0, 0, seed=77)
+    rng = np.random.default_rng(78)
+    T = len(w.slot_mapping)
+    key, value = W.normal_words(rng, (T, 2, 16), "bf16"), W.normal_words(rng, (T, 2, 16), "bf16")
+    cache = W.normal_words(rng, shape.cache_shape[1:], "bf16")
+    indptr, indices = W.paged_metadata(w.tables.tables)
+    batch = np.repeat(np.arange(5, dtype=np.int32), 40)
+    # recover each token's position from its slot and table
+    pos = np.empty(T, np.int32)
+    for i, s in enumerate(w.slot_mapping):
+        t = w.tables.tables[batch[i]]
+        pos[i] = int(np.nonzero(t == s // 16)[0][0]) * 16 + s % 16
+    a, b = cache.copy(), cache.copy()
+    cache_oracle.append_paged_kv_cache(key, value, batch, pos, a, indices, indptr)
+    cache_oracle.reshape_and_cache(key, value, b, w.slot_mapping)
+    assert np.array_equal(a, b) and not np.array_equal(a, cache)
+    batch[3] = -1
+    c = cache.copy()
+    cache_oracle.append_paged_kv_cache(key, value, batch, pos, c, indices, indptr)
+    slots = w.slot_mapping.copy()
+    slots[3] = -1
+    d = cache.copy()
+    cache_oracle.reshape_and_cache(key, value, d, slots)
+    assert np.array_equal(c, d)
