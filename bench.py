@@ -338,8 +338,13 @@ def run_ours(args):
             },
             "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": peak_gbs,
                          "unit": "GB/s", "frac": round(achieved / peak_gbs, 4),
-                         "peak_kind": peak_kind, "traffic": None,
-                         "kernel": "write_rows_vec", "algorithmic_bytes_per_launch": step_bytes},
+                         "peak_kind": peak_kind,
+                         # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this
+                         # workload under ncu (profiles/write_rows_direct_decode_write_small.md):
+                         # the sources are read once; the scattered stores are still dirty in
+                         # L2 when the kernel ends and reach DRAM during the next launches
+                         "traffic": 34.8e6, "traffic_unit": "bytes per launch, in-kernel",
+                         "kernel": "write_rows_direct", "algorithmic_bytes_per_launch": step_bytes},
             "e2e": {k: (round(v, 3) if isinstance(v, float) else v) for k, v in e2e.items()},
             "gpu_launches": launches,
             "clocks": sampler.summary(),

@@ -56,17 +56,21 @@ typedef enum lms_status {
 #define LMS_SWAP_OUT 0 /* GPU  -> host (kv_worker.py "save")  */
 #define LMS_SWAP_IN 1  /* host -> GPU  (kv_worker.py "load")  */
 
-/* Tunables for lms_set_tuning (values <= 0 restore the built-in choice). */
-#define LMS_TUNE_WRITE_VARIANT 1 /* 0 = 16-byte ld/st, 1 = 32-byte ld/st, 2 = bulk-copy (TMA) rows */
+/* Tunables for lms_set_tuning (a negative value restores the built-in choice; for the
+ * non-variant keys 0 does too). */
+#define LMS_TUNE_WRITE_VARIANT 1 /* 0 = tiled 16-byte ld/st, 1 = tiled 32-byte, 2 = bulk-copy (TMA) rows,
+                                    3 = untiled one-vector-per-thread 32-byte, 4 = untiled 16-byte */
 #define LMS_TUNE_WRITE_TILE_BYTES 2 /* payload bytes read per CTA of the cache write */
-#define LMS_TUNE_COPY_VARIANT 3  /* 0 = 16-byte ld/st, 1 = 32-byte ld/st, 2 = bulk-copy (TMA) */
+#define LMS_TUNE_COPY_VARIANT 3  /* 0 = persistent 16-byte ld/st, 1 = persistent 32-byte, 2 = bulk-copy (TMA),
+                                    3 = untiled one-vector-per-thread */
 #define LMS_TUNE_COPY_CTAS_PER_SM 4
 #define LMS_TUNE_SWAP_OUT_CTAS 5 /* total CTAs of the GPU->host kernel */
 #define LMS_TUNE_SWAP_IN_CTAS 6  /* total CTAs of the host->GPU kernel */
 #define LMS_TUNE_XFER_CTAS_PER_SM 7
-#define LMS_TUNE_XFER_VARIANT 8  /* 0 = 16-byte ld/st, 1 = 32-byte, 2 = bulk-copy */
+#define LMS_TUNE_XFER_VARIANT 8  /* as LMS_TUNE_COPY_VARIANT */
 #define LMS_TUNE_WRITE_VPT 9     /* vectors per thread per pipeline batch of the cache write: 2, 4, 8 */
-#define LMS_TUNE__COUNT 10
+#define LMS_TUNE_SWAP_VARIANT 10 /* as LMS_TUNE_COPY_VARIANT, both directions */
+#define LMS_TUNE__COUNT 11
 
 /* Library version (LMS_VERSION of the build). */
 int lms_version(void);

@@ -165,8 +165,7 @@ int write_launch(WriteParams p, void* stream) {
   if (int rc = device_state(&ds)) return rc;
   p.err = ds->err;
   p.checks = g_checks.load(std::memory_order_relaxed);
-  // 32-byte vectors where alignment allows (launch_write falls back to 16 bytes otherwise)
-  const int variant = tuned_variant(LMS_TUNE_WRITE_VARIANT, 1);
+  const int variant = tuned_variant(LMS_TUNE_WRITE_VARIANT, -1);  // -1: launch_write chooses
   const int tile = tuned(LMS_TUNE_WRITE_TILE_BYTES, 0);
   const int vpt = tuned(LMS_TUNE_WRITE_VPT, 2);
   LMS_CUDA(launch_write(p, variant, tile, vpt, ds->sms, (cudaStream_t)stream));
@@ -351,10 +350,10 @@ int lms_init_device(void) {
 
 int lms_set_tuning(int key, int value) {
   if (key <= 0 || key >= LMS_TUNE__COUNT) return LMS_ERR_RANGE;
-  const bool is_variant = key == LMS_TUNE_WRITE_VARIANT ||
-                          key == LMS_TUNE_COPY_VARIANT || key == LMS_TUNE_XFER_VARIANT;
+  const bool is_variant = key == LMS_TUNE_WRITE_VARIANT || key == LMS_TUNE_COPY_VARIANT ||
+                          key == LMS_TUNE_XFER_VARIANT || key == LMS_TUNE_SWAP_VARIANT;
   if (is_variant) {
-    if (value > 2) return LMS_ERR_RANGE;
+    if (value > (key == LMS_TUNE_WRITE_VARIANT ? 4 : 3)) return LMS_ERR_RANGE;
     g_tuning[key].store(value < 0 ? 0 : value + 1);
   } else {
     g_tuning[key].store(value < 0 ? 0 : value);
@@ -364,8 +363,8 @@ int lms_set_tuning(int key, int value) {
 
 int lms_get_tuning(int key) {
   if (key <= 0 || key >= LMS_TUNE__COUNT) return LMS_ERR_RANGE;
-  const bool is_variant = key == LMS_TUNE_WRITE_VARIANT ||
-                          key == LMS_TUNE_COPY_VARIANT || key == LMS_TUNE_XFER_VARIANT;
+  const bool is_variant = key == LMS_TUNE_WRITE_VARIANT || key == LMS_TUNE_COPY_VARIANT ||
+                          key == LMS_TUNE_XFER_VARIANT || key == LMS_TUNE_SWAP_VARIANT;
   const int v = g_tuning[key].load();
   return is_variant ? v - 1 : v;
 }
@@ -503,7 +502,7 @@ int lms_copy_blocks(void* kv, int64_t layer_stride, int64_t block_stride,
   return chunk_copy(kv, layer_stride, block_stride, kv, layer_stride,
                     block_stride, chunk_bytes, num_layers, pairs, n_pairs,
                     num_blocks, num_blocks, /*layer_major=*/1, kWhereCopyBlocks,
-                    tuned_variant(LMS_TUNE_COPY_VARIANT, 1), /*policy=*/1,
+                    tuned_variant(LMS_TUNE_COPY_VARIANT, 3), /*policy=*/1,
                     sm_count() * per_sm, stream);
 }
 
@@ -526,12 +525,14 @@ int lms_swap_blocks(int direction, void* gpu, int64_t gpu_layer_stride,
     return chunk_copy(g, gpu_layer_stride, gpu_block_stride, h,
                       host_layer_stride, host_block_stride, chunk_bytes, nl,
                       pairs, n_pairs, num_gpu_blocks, num_host_blocks,
-                      /*layer_major=*/0, kWhereSwapOut, 0, 0,
+                      /*layer_major=*/0, kWhereSwapOut,
+                      tuned_variant(LMS_TUNE_SWAP_VARIANT, 0), 0,
                       tuned(LMS_TUNE_SWAP_OUT_CTAS, sm_count() * 2), stream);
   return chunk_copy(h, host_layer_stride, host_block_stride, g,
                     gpu_layer_stride, gpu_block_stride, chunk_bytes, nl, pairs,
                     n_pairs, num_host_blocks, num_gpu_blocks,
-                    /*layer_major=*/0, kWhereSwapIn, 0, 0,
+                    /*layer_major=*/0, kWhereSwapIn,
+                    tuned_variant(LMS_TUNE_SWAP_VARIANT, 0), 0,
                     tuned(LMS_TUNE_SWAP_IN_CTAS, sm_count() * 4), stream);
 }
 
@@ -547,7 +548,7 @@ int lms_transfer_blocks(const void* src, int64_t src_layer_stride,
                     dst_layer_stride, dst_block_stride, chunk_bytes, num_layers,
                     pairs, n_pairs, num_src_blocks, num_dst_blocks,
                     /*layer_major=*/1, kWhereTransfer,
-                    tuned_variant(LMS_TUNE_XFER_VARIANT, 0), 0,
+                    tuned_variant(LMS_TUNE_XFER_VARIANT, 3), 0,
                     sm_count() * per_sm, stream);
 }
 
@@ -592,7 +593,7 @@ int lms_copy_blocks_host_static(void* kv, int64_t layer_stride, int64_t block_st
   p.where = kWhereCopyBlocks;
   p.checks = 0;
   const int per_sm = tuned(LMS_TUNE_COPY_CTAS_PER_SM, 2);
-  LMS_CUDA(launch_chunk_copy(p, tuned_variant(LMS_TUNE_COPY_VARIANT, 1), /*policy=*/1,
+  LMS_CUDA(launch_chunk_copy(p, tuned_variant(LMS_TUNE_COPY_VARIANT, 3), /*policy=*/1,
                              st->sms * per_sm, (cudaStream_t)stream));
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return LMS_OK;

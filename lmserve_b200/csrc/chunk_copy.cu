@@ -113,6 +113,54 @@ chunk_copy_vec(const CopyParams p) {
   }
 }
 
+// Untiled form: thread i owns vector i of the flattened (layer | pair, vector-in-chunk)
+// space.  No persistent loop, no shared memory; the pair entry is a broadcast load.
+template <class Vec, int THREADS, int POLICY>
+__global__ void __launch_bounds__(THREADS)
+chunk_copy_direct(const CopyParams p, const int chunk_vecs, const int chunk_shift,
+                  const long long n_vec_total) {
+  const long long v = (long long)blockIdx.x * THREADS + threadIdx.x;
+  if (v >= n_vec_total) return;
+  long long q;
+  int c;
+  if (chunk_shift >= 0) {
+    q = v >> chunk_shift;
+    c = (int)(v & (chunk_vecs - 1));
+  } else {
+    q = v / chunk_vecs;
+    c = (int)(v - q * chunk_vecs);
+  }
+  long long pair, layer;
+  if (p.layer_major) {
+    layer = q / p.n_pairs;
+    pair = q - layer * p.n_pairs;
+  } else {
+    pair = q / p.num_layers;
+    layer = q - pair * p.num_layers;
+  }
+  const longlong2 sd = reinterpret_cast<const longlong2*>(p.pairs)[pair];
+  if (p.checks) {
+    if (sd.x < 0 || (p.num_src_blocks > 0 && sd.x >= p.num_src_blocks)) {
+      if (c == 0) report(p.err, kErrBadSrcBlock, p.where, pair, sd.x);
+      return;
+    }
+    if (sd.y < 0 || (p.num_dst_blocks > 0 && sd.y >= p.num_dst_blocks)) {
+      if (c == 0) report(p.err, kErrBadDstBlock, p.where, pair, sd.y);
+      return;
+    }
+  }
+  const char* s = p.src + layer * p.src_layer + sd.x * p.src_block + (long long)c * Vec::kBytes;
+  char* d = p.dst + layer * p.dst_layer + sd.y * p.dst_block + (long long)c * Vec::kBytes;
+  Vec r;
+  if (POLICY == 1) {
+    ld_hint(r, s, policy_evict_last());
+    st_hint(d, r, policy_evict_first());
+  } else {
+    ld(r, s);
+    st(d, r);
+  }
+}
+
 // Bulk (TMA) form: a slice is what ONE lane moves; 32 consecutive units are a
 // warp-task.  Every lane issues one bulk load into its own shared-memory
 // buffer, the warp waits on one mbarrier, every lane issues one bulk store.
@@ -189,6 +237,22 @@ cudaError_t launch_vec(CopyParams p, int grid_ctas, cudaStream_t stream) {
   return cudaGetLastError();
 }
 
+template <class Vec, int POLICY>
+cudaError_t launch_direct(const CopyParams& p, cudaStream_t stream) {
+  constexpr int THREADS = 256;
+  const int chunk_vecs = p.chunk_bytes / Vec::kBytes;
+  int shift = -1;
+  if ((chunk_vecs & (chunk_vecs - 1)) == 0) {
+    shift = 0;
+    while ((1 << shift) < chunk_vecs) ++shift;
+  }
+  const long long n_vec = (long long)p.num_layers * p.n_pairs * chunk_vecs;
+  const long long ctas = (n_vec + THREADS - 1) / THREADS;
+  if (ctas > 0x7fffffffll) return cudaErrorInvalidConfiguration;
+  chunk_copy_direct<Vec, THREADS, POLICY><<<(unsigned)ctas, THREADS, 0, stream>>>(p, chunk_vecs, shift, n_vec);
+  return cudaGetLastError();
+}
+
 }  // namespace
 
 cudaError_t launch_chunk_copy(const CopyParams& p_in, int variant, int policy,
@@ -200,6 +264,11 @@ cudaError_t launch_chunk_copy(const CopyParams& p_in, int variant, int policy,
                         (uintptr_t)(p.src_layer | p.src_block | p.dst_layer |
                                     p.dst_block | (long long)p.chunk_bytes);
   if (variant == 1 && (a32 & 31u) != 0) variant = 0;
+  if (variant == 3) {
+    if ((a32 & 31u) != 0)
+      return policy == 1 ? launch_direct<V16, 1>(p, stream) : launch_direct<V16, 0>(p, stream);
+    return policy == 1 ? launch_direct<V32, 1>(p, stream) : launch_direct<V32, 0>(p, stream);
+  }
 
   if (variant == 2) {
     constexpr int WARPS = 2;

@@ -6,12 +6,14 @@
 // HBM bandwidth: 2 * row_bytes read and 2 * row_bytes written per live token
 // per layer.
 //
-// Two implementations share one parameter block:
+// Three implementations share one parameter block (write_rows_direct is the default):
 //   * write_rows_vec  - a CTA owns a tile of tokens of one layer.  Slot loads and
 //     the first batch of payload loads are issued together; the slots are then
 //     turned into destination byte offsets once, in shared memory, and the tile
 //     is streamed as a two-stage software pipeline of 16- or 32-byte vectors
 //     (loads of batch b+1 in flight while batch b is stored).
+//   * write_rows_direct - no tile and no shared memory: thread i owns vector i of
+//     the whole launch, issues its index loads and payload load together, stores.
 //   * write_rows_bulk - every lane of a warp owns one piece of a row and moves
 //     it with a bulk (TMA) copy global -> shared -> global; the warp shares one
 //     mbarrier.  Almost no instructions per byte.
@@ -170,6 +172,46 @@ write_rows_vec(const WriteParams p, const int row_vecs, const int row_shift) {
   }
 }
 
+// Small launches (one layer of a decode step is 2 MiB): no tile, no shared memory, no
+// barrier.  Thread i owns vector i of the flattened (layer, token, K|V, vector-in-row) space;
+// it issues its index loads and its payload load together, walks the page table if there is
+// one, and stores.  Lanes of a warp that share a token read the same index words (one
+// broadcast transaction).  Launch + one memory round trip + the store is all that is left.
+template <class Vec, int THREADS, bool POW2>
+__global__ void __launch_bounds__(THREADS)
+write_rows_direct(const WriteParams p, const int row_vecs, const int row_shift,
+                  const long long n_vec_total) {
+  const long long v = (long long)blockIdx.x * THREADS + threadIdx.x;
+  if (v >= n_vec_total) return;
+  // v = ((layer * T + t) * 2 + kv) * row_vecs + c
+  long long q;
+  int c;
+  if (POW2) {
+    c = (int)(v & (row_vecs - 1));
+    q = v >> row_shift;
+  } else {
+    q = v / row_vecs;
+    c = (int)(v - q * row_vecs);
+  }
+  const int kv = (int)(q & 1);
+  q >>= 1;
+  const int layer = (int)(q / p.num_tokens);
+  const int t = (int)(q - (long long)layer * p.num_tokens);
+
+  const SlotRaw raw = slot_fetch_begin(p, layer, t);
+  const char* src = (kv ? p.value + (long long)layer * p.val_layer + (long long)t * p.val_tok
+                        : p.key + (long long)layer * p.key_layer + (long long)t * p.key_tok) +
+                    (long long)c * Vec::kBytes;
+  Vec r;
+  ld(r, src);
+  const long long off =
+      slot_offset(p, slot_fetch_end(p, raw), (long long)layer * p.slot_layer + t);
+  if (off >= 0)
+    st((kv ? p.vcache : p.kcache) + (long long)layer * p.cache_layer + off +
+           (long long)c * Vec::kBytes,
+       r);
+}
+
 // One piece per lane per iteration; a warp-task is 32 consecutive pieces of
 // the flattened (layer, token, K|V, piece) index space.
 template <int WARPS>
@@ -283,6 +325,23 @@ cudaError_t launch_vec(WriteParams p, int tile_bytes, int sms, cudaStream_t stre
 }
 
 template <class Vec>
+cudaError_t launch_direct(const WriteParams& p, cudaStream_t stream) {
+  constexpr int THREADS = 256;
+  const int row_vecs = p.row_bytes / Vec::kBytes;
+  const int row_shift = ilog2_exact(row_vecs);
+  const long long n_vec = (long long)p.num_layers * p.num_tokens * 2 * row_vecs;
+  const long long ctas = (n_vec + THREADS - 1) / THREADS;
+  if (ctas > 0x7fffffffll) return cudaErrorInvalidConfiguration;
+  if (row_shift >= 0)
+    write_rows_direct<Vec, THREADS, true>
+        <<<(unsigned)ctas, THREADS, 0, stream>>>(p, row_vecs, row_shift, n_vec);
+  else
+    write_rows_direct<Vec, THREADS, false>
+        <<<(unsigned)ctas, THREADS, 0, stream>>>(p, row_vecs, row_shift, n_vec);
+  return cudaGetLastError();
+}
+
+template <class Vec>
 cudaError_t launch_vec_vpt(const WriteParams& p, int tile_bytes, int vpt, int sms,
                            cudaStream_t stream) {
   if (vpt == 4) return launch_vec<Vec, 4>(p, tile_bytes, sms, stream);
@@ -306,7 +365,18 @@ cudaError_t launch_write(const WriteParams& p_in, int variant, int tile_bytes,
                               (long long)p.row_bytes;
     return ((ptrs | (uintptr_t)strides) & 31u) == 0;
   };
-  if (variant == 1 && !aligned32()) variant = 0;
+  const bool a32 = aligned32();
+  if (variant < 0) {
+    // Built-in choice, from measurement on B200: the untiled 32-byte kernel is the fastest
+    // at every size from one layer of a decode step (2 MiB) to a 28-layer prefill chunk
+    // (3.5 GiB).  Rows that cannot take 32-byte accesses use the untiled 16-byte kernel for
+    // small launches and the tiled one for large launches.
+    const long long total = (long long)p.num_layers * p.num_tokens * 2 * p.row_bytes;
+    variant = a32 ? 3 : (total <= (16ll << 20) ? 4 : 0);
+  }
+  if (variant == 1 && !a32) variant = 0;
+  if (variant == 3) return a32 ? launch_direct<V32>(p, stream) : launch_direct<V16>(p, stream);
+  if (variant == 4) return launch_direct<V16>(p, stream);
 
   if (variant == 2) {
     // piece = the largest power-of-two divisor of the row, capped at 1 KiB

@@ -27,8 +27,34 @@ from .. import _lib
 PairList = Union[Sequence[Tuple[int, int]], np.ndarray, torch.Tensor]
 
 
+try:  # the raw handle of the current stream without building a Stream object
+    _raw_stream = torch._C._cuda_getCurrentRawStream
+except AttributeError:  # pragma: no cover - older / newer torch
+    _raw_stream = None
+
+
 def _stream_ptr(device: torch.device) -> int:
+    if _raw_stream is not None:
+        return _raw_stream(device.index if device.index is not None else torch.cuda.current_device())
     return torch.cuda.current_stream(device).cuda_stream
+
+
+class _OnDevice:
+    """``with torch.cuda.device(dev)`` that costs nothing when `dev` is already current."""
+
+    __slots__ = ("_guard",)
+
+    def __init__(self, device: torch.device):
+        idx = device.index
+        self._guard = None if idx is None or idx == torch.cuda.current_device() else torch.cuda.device(idx)
+
+    def __enter__(self):
+        if self._guard is not None:
+            self._guard.__enter__()
+
+    def __exit__(self, *exc):
+        if self._guard is not None:
+            self._guard.__exit__(*exc)
 
 
 def _require_cuda(name: str, t: torch.Tensor) -> None:
@@ -145,7 +171,7 @@ def fill_key_cache(
         raise ValueError("slot_mapping must have one entry per token")
     slots = _slots_i64(slot_mapping, dev)
     num_slots = key_cache.numel() * key_cache.element_size() // row_bytes
-    with torch.cuda.device(dev):
+    with _OnDevice(dev):
         _lib.check(_lib.lib().lms_reshape_and_cache(
             key.data_ptr(), value.data_ptr(), k_tok, v_tok,
             key_cache.data_ptr(), value_cache.data_ptr(),
@@ -216,54 +242,71 @@ def append_paged_kv_cache(
     """
     if kv_layout != "NHD":
         raise ValueError("only the NHD layout (LMServe's) is supported")
-    _require_cuda("append_key", append_key)
-    _require_cuda("append_value", append_value)
-    if isinstance(paged_kv_cache, (tuple, list)):
-        k_cache, v_cache = paged_kv_cache
-        _require_cuda("k_cache", k_cache)
-        _require_cuda("v_cache", v_cache)
-        if k_cache.dim() != 4 or k_cache.shape != v_cache.shape or k_cache.stride() != v_cache.stride():
-            raise ValueError("k_cache and v_cache must both be [num_pages, page_size, H, D]")
-        NB, BS, H, D = k_cache.shape
-        block_stride = k_cache.stride(0) * k_cache.element_size()
-        page_ok = NB == 0 or k_cache[0].is_contiguous()
-        kptr, vptr, cdtype, dev = k_cache.data_ptr(), v_cache.data_ptr(), k_cache.dtype, k_cache.device
-    else:
-        _require_cuda("paged_kv_cache", paged_kv_cache)
-        if paged_kv_cache.dim() != 5 or paged_kv_cache.shape[1] != 2:
+    # This runs once per layer per step: checks are kept to attribute reads.
+    if type(paged_kv_cache) is torch.Tensor:
+        cache = paged_kv_cache
+        cshape = cache.shape
+        if len(cshape) != 5 or cshape[1] != 2:
             raise ValueError("paged_kv_cache must be [num_pages, 2, page_size, H, D]")
-        NB, _, BS, H, D = paged_kv_cache.shape
-        block_stride = paged_kv_cache.stride(0) * paged_kv_cache.element_size()
-        page_ok = NB == 0 or paged_kv_cache[0].is_contiguous()
-        kptr = paged_kv_cache.data_ptr()
-        vptr = kptr + BS * H * D * paged_kv_cache.element_size()
-        cdtype, dev = paged_kv_cache.dtype, paged_kv_cache.device
-    if not page_ok:
-        raise ValueError("each cache page must be contiguous")
-    k_tok, row_bytes = _row_layout("append_key", append_key)
-    v_tok, v_row = _row_layout("append_value", append_value)
-    T = append_key.shape[0]
-    if tuple(append_key.shape[1:]) != (H, D) or append_value.shape != append_key.shape:
-        raise ValueError("append_key / append_value do not match the cache's [H, D]")
+        NB, _, BS, H, D = cshape
+        cstride = cache.stride()
+        es = cache.element_size()
+        if cstride[4] != 1 or cstride[3] != D or cstride[2] != H * D or cstride[1] != BS * H * D:
+            raise ValueError("each cache page must be contiguous")
+        block_stride = cstride[0] * es
+        kptr = cache.data_ptr()
+        vptr = kptr + BS * H * D * es
+    else:
+        k_cache, v_cache = paged_kv_cache
+        cache = k_cache
+        cshape = k_cache.shape
+        if len(cshape) != 4 or cshape != v_cache.shape or k_cache.stride() != v_cache.stride():
+            raise ValueError("k_cache and v_cache must both be [num_pages, page_size, H, D]")
+        NB, BS, H, D = cshape
+        cstride = k_cache.stride()
+        es = k_cache.element_size()
+        if cstride[3] != 1 or cstride[2] != D or cstride[1] != H * D or not v_cache.is_cuda:
+            raise ValueError("each cache page must be contiguous and on the GPU")
+        if v_cache.dtype != k_cache.dtype:
+            raise TypeError("k_cache and v_cache must have the same dtype")
+        block_stride = cstride[0] * es
+        kptr, vptr = k_cache.data_ptr(), v_cache.data_ptr()
+    if not cache.is_cuda:
+        raise RuntimeError(
+            f"paged_kv_cache must live on a CUDA device (got {cache.device}); the cache ops have no CPU path")
+    dev = cache.device
+    kshape = append_key.shape
+    if len(kshape) != 3 or kshape[1] != H or kshape[2] != D or append_value.shape != kshape:
+        raise ValueError("append_key / append_value must be [T, H, D] matching the cache")
+    T = kshape[0]
+    ks, vs = append_key.stride(), append_value.stride()
+    if ks[2] != 1 or vs[2] != 1 or (H > 1 and (ks[1] != D or vs[1] != D)):
+        raise ValueError("each token's [H, D] row must be contiguous")
+    cdtype = cache.dtype
     if append_key.dtype != cdtype or append_value.dtype != cdtype:
         raise TypeError("cache dtype must match key/value dtype (bytes are copied, not converted)")
-    idx = []
+    if append_key.device != dev or append_value.device != dev:
+        raise RuntimeError("append_key / append_value must be on the cache's device; the cache ops have no CPU path")
+    i32 = torch.int32
     for name, t in (("batch_indices", batch_indices), ("positions", positions),
                     ("kv_indices", kv_indices), ("kv_indptr", kv_indptr)):
-        _require_cuda(name, t)
-        if t.dtype != torch.int32:
+        if t.dtype != i32:
             raise TypeError(f"{name} must be int32 (got {t.dtype})")
-        idx.append(t.contiguous())
-    if idx[0].numel() != T or idx[1].numel() != T:
+        if t.device != dev or not t.is_contiguous():
+            raise ValueError(f"{name} must be a contiguous tensor on the cache's device")
+    if batch_indices.numel() != T or positions.numel() != T:
         raise ValueError("batch_indices and positions need one entry per appended token")
     if T == 0:
         return
-    with torch.cuda.device(dev):
-        _lib.check(_lib.lib().lms_append_paged_kv_cache(
-            append_key.data_ptr(), append_value.data_ptr(), k_tok, v_tok, 0, 0,
-            idx[0].data_ptr(), idx[1].data_ptr(), kptr, vptr, 0, block_stride, row_bytes,
-            idx[2].data_ptr(), idx[3].data_ptr(), T, 1, row_bytes, BS, NB,
-            _stream_ptr(dev)))
+    row_bytes = H * D * es
+    with _OnDevice(dev):
+        rc = _lib.lib().lms_append_paged_kv_cache(
+            append_key.data_ptr(), append_value.data_ptr(), ks[0] * es, vs[0] * es, 0, 0,
+            batch_indices.data_ptr(), positions.data_ptr(), kptr, vptr, 0, block_stride,
+            row_bytes, kv_indices.data_ptr(), kv_indptr.data_ptr(), T, 1, row_bytes, BS, NB,
+            _stream_ptr(dev))
+    if rc:
+        _lib.check(rc)
 
 
 def _prepare_write(key, value, kv_caches, slot_mapping):
@@ -305,7 +348,7 @@ def _prepare_write(key, value, kv_caches, slot_mapping):
 
 def _write_layers(key, value, kv_caches, slot_mapping) -> None:
     dev, _keep, args = _prepare_write(key, value, kv_caches, slot_mapping)
-    with torch.cuda.device(dev):
+    with _OnDevice(dev):
         _lib.check(_lib.lib().lms_reshape_and_cache_layers(*args, _stream_ptr(dev)))
 
 
@@ -386,7 +429,7 @@ def copy_blocks(
         return
     L_ = _lib.lib()
     fn = L_.lms_copy_blocks if on_device else L_.lms_copy_blocks_host
-    with torch.cuda.device(dev):
+    with _OnDevice(dev):
         _lib.check(fn(kv_caches.data_ptr(), layer_stride, block_stride, chunk, L,
                       ptr, n, NB, _stream_ptr(dev)))
 
@@ -410,7 +453,7 @@ def copy_blocks_no_alloc(
     arr = flatten_block_map(src_to_dst)
     if arr.shape[0] == 0:
         return
-    with torch.cuda.device(dev):
+    with _OnDevice(dev):
         _lib.check(_lib.lib().lms_copy_blocks_host_static(
             kv_caches.data_ptr(), layer_stride, block_stride, chunk, L,
             arr.ctypes.data, arr.shape[0], _stream_ptr(dev)))
@@ -448,7 +491,7 @@ def swap_blocks(
         return
     L_ = _lib.lib()
     fn = L_.lms_swap_blocks if on_device else L_.lms_swap_blocks_host
-    with torch.cuda.device(dev):
+    with _OnDevice(dev):
         _lib.check(fn(
             _lib.LMS_SWAP_OUT if direction == "out" else _lib.LMS_SWAP_IN,
             gpu_kv_caches.data_ptr(), layer_stride, block_stride,
@@ -478,7 +521,7 @@ def transfer_blocks(
         dL, dNB, d_layer, d_block, d_chunk = _cache_geometry(dst_kv_caches)
         dst_ptr = dst_kv_caches.data_ptr()
         if dst_kv_caches.device != dev:
-            with torch.cuda.device(dev):
+            with _OnDevice(dev):
                 _lib.check(_lib.lib().lms_peer_enable(dst_kv_caches.device.index))
     else:
         dL, dNB, d_layer, d_block, d_chunk = (dst_kv_caches.num_layers, dst_kv_caches.num_blocks,
@@ -492,6 +535,6 @@ def transfer_blocks(
         return
     L_ = _lib.lib()
     fn = L_.lms_transfer_blocks if on_device else L_.lms_transfer_blocks_host
-    with torch.cuda.device(dev):
+    with _OnDevice(dev):
         _lib.check(fn(src_kv_caches.data_ptr(), s_layer, s_block, dst_ptr, d_layer, d_block,
                       chunk, L, ptr, n, NB, dNB, _stream_ptr(dev)))

@@ -18,22 +18,24 @@ from oracle import cache_oracle
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
-VARIANTS = [0, 1, 2]  # 16-byte vectors, 32-byte vectors, bulk (TMA) copies
+VARIANTS = [0, 1, 2, 3, 4]  # tiled 16/32-byte vectors, bulk (TMA) copies, untiled 32/16-byte
 
 
 @pytest.fixture(autouse=True)
 def _reset_tuning():
     yield
     L = _lib.lib()
-    for key in range(1, 10):
+    for key in range(1, 11):
         L.lms_set_tuning(key, -1)
     L.lms_set_debug_checks(0)
 
 
 def set_variant(v):
+    """Write-kernel variant v; the copy kernels have variants 0..2 only."""
     L = _lib.lib()
-    for key in (_lib.TUNE_WRITE_VARIANT, _lib.TUNE_COPY_VARIANT, _lib.TUNE_XFER_VARIANT):
-        assert L.lms_set_tuning(key, v) == 0
+    assert L.lms_set_tuning(_lib.TUNE_WRITE_VARIANT, v) == 0
+    for key in (_lib.TUNE_COPY_VARIANT, _lib.TUNE_XFER_VARIANT):
+        assert L.lms_set_tuning(key, min(v, 3)) == 0
 
 
 # ----------------------------------------------------------------- golden vectors

@@ -20,7 +20,7 @@ DEV = "cuda:0"
 @pytest.fixture(autouse=True)
 def _reset_tuning():
     yield
-    for key in range(1, 10):
+    for key in range(1, 11):
         _lib.lib().lms_set_tuning(key, -1)
 
 
@@ -29,9 +29,11 @@ def make_gpu_cache(shape, seed):
     return words, to_tensor(words, shape.dtype, DEV)
 
 
+@pytest.mark.parametrize("variant", [0, 1, 2, 3])
 @pytest.mark.parametrize("ctas", [0, 8, 300])
-def test_swap_out_in_vs_oracle(ctas):
+def test_swap_out_in_vs_oracle(ctas, variant):
     L = _lib.lib()
+    L.lms_set_tuning(_lib.TUNE_SWAP_VARIANT, variant)
     L.lms_set_tuning(_lib.TUNE_SWAP_OUT_CTAS, ctas)
     L.lms_set_tuning(_lib.TUNE_SWAP_IN_CTAS, ctas)
     shape = W.SHAPES["llama31_8b_swap"].scaled(num_layers=3, num_blocks=64)
@@ -112,7 +114,7 @@ def test_kvworker_copy_kv_with_layer_events():
         worker.close()
 
 
-@pytest.mark.parametrize("variant", [0, 1, 2])
+@pytest.mark.parametrize("variant", [0, 1, 2, 3])
 def test_transfer_blocks_same_device_vs_oracle(variant):
     _lib.lib().lms_set_tuning(_lib.TUNE_XFER_VARIANT, variant)
     shape = W.SHAPES["llama31_70b_tp8"].scaled(num_layers=6, num_blocks=300)
