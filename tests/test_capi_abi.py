@@ -107,3 +107,27 @@ def test_check_raises_with_message():
 
 def test_launch_count_is_zero_without_launches():
     assert _lib.lib().lms_launch_count() >= 0
+
+
+def test_write_plan_and_paged_argument_errors():
+    L = _lib.lib()
+    h = ctypes.c_void_p()
+    mk = lambda **kw: L.lms_write_plan_create(
+        kw.get("key", A), A, 1024, 1024, 0, 0, A, A, 0, 32768, kw.get("slot_stride", 1024),
+        kw.get("slots", A), 0, kw.get("T", 4), 1, kw.get("row", 1024), 16, 0,
+        ctypes.byref(h) if kw.get("out", True) else None)
+    assert mk(out=False) == _lib.LMS_ERR_NULL
+    assert mk(key=None) == _lib.LMS_ERR_NULL and not h.value
+    assert mk(row=1000) == _lib.LMS_ERR_ALIGN
+    assert mk(T=-1) == _lib.LMS_ERR_RANGE
+    assert L.lms_write_plan_run(None, None) == _lib.LMS_ERR_NULL
+    assert L.lms_write_plan_destroy(None) == _lib.LMS_OK
+    f = L.lms_append_paged_kv_cache
+    paged = lambda **kw: f(A, A, 1024, 1024, 0, 0, kw.get("bi", A), A, A, A, 0, 32768, 1024,
+                           kw.get("ind", A), A, kw.get("T", 4), 1, 1024, 16, kw.get("nb", 8), None)
+    assert paged(T=0) == _lib.LMS_OK
+    assert paged(bi=None) == _lib.LMS_ERR_NULL
+    assert paged(ind=A + 2) == _lib.LMS_ERR_ALIGN
+    assert paged(nb=-1) == _lib.LMS_ERR_RANGE
+    assert L.lms_copy_blocks_host_static(A, 1 << 20, 4096, 4096, 2, A,
+                                         _lib.LMS_STATIC_MAX_PAIRS + 1, None) == _lib.LMS_ERR_TOO_LARGE
