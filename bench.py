@@ -343,7 +343,7 @@ def run_ours(args):
                          # workload under ncu (profiles/write_rows_direct_decode_write_small.md):
                          # the sources are read once; the scattered stores are still dirty in
                          # L2 when the kernel ends and reach DRAM during the next launches
-                         "traffic": 34.8e6, "traffic_unit": "bytes per launch, in-kernel",
+                         "traffic": 34.9e6, "traffic_unit": "bytes per launch, in-kernel",
                          "kernel": "write_rows_direct", "algorithmic_bytes_per_launch": step_bytes},
             "e2e": {k: (round(v, 3) if isinstance(v, float) else v) for k, v in e2e.items()},
             "gpu_launches": launches,
