@@ -202,6 +202,41 @@ int lms_append_paged_kv_cache(const void* key, const void* value,
                               int32_t block_size, int64_t num_blocks, void* stream);
 
 /*
+ * Rotary position embedding, optionally fused with the cache write that follows it in the
+ * attention layer — replaces
+ *   rotary_pos_emb               runtime/worker/llm_worker/ops/rotary_embedding_ops.py:8-38
+ *   apply_rotary_pos_emb_kernel  runtime/worker/llm_worker/ops/triton/rotary_embedding.py:5-66
+ * and, when key_cache / value_cache are given, the cache write of
+ *   runtime/worker/llm_worker/models/layers/attention.py:76-85
+ * in the same launch (call order in runtime/worker/llm_worker/models/llama.py:156-167).
+ *
+ * query [T, num_heads*head_dim], key / value [T, num_kv_heads*head_dim] (token strides in
+ * bytes), positions int32 (positions_are_int64 = 0) or int64 [T], cos_sin_cache
+ * [max_position, 2*head_dim] = the cos row then the sin row of a position (row stride in
+ * bytes).  For every head, x = first half, y = second half:
+ *   out_x = x*cos[i] - y*sin[i],  out_y = y*cos[D/2+i] + x*sin[D/2+i],
+ * every product and sum rounded to the element type (dtype 0 = fp16, 1 = bf16), which is the
+ * arithmetic of the Triton kernel evaluated one operation at a time.  Rotated Q goes to q_out;
+ * rotated K goes to k_out if it is not NULL and, if the caches are not NULL, to the key-cache
+ * row of slot_mapping[t]; V is copied to the value-cache row.  Cache addressing, the slot < 0
+ * padding rule and num_slots are those of lms_reshape_and_cache.  Only the full rotary
+ * dimension (rotary_dim == head_dim, a multiple of 16) is supported, which covers the Llama
+ * and Qwen2 models of the reference.  max_position: debug checks only (0 = unknown).
+ */
+int lms_rope_and_cache(const void* query, const void* key, const void* value,
+                       int64_t query_token_stride, int64_t key_token_stride,
+                       int64_t value_token_stride, const void* positions,
+                       int32_t positions_are_int64, const void* cos_sin_cache,
+                       int64_t cos_sin_row_stride, void* q_out,
+                       int64_t q_out_token_stride, void* k_out,
+                       int64_t k_out_token_stride, void* key_cache,
+                       void* value_cache, int64_t block_stride, int64_t slot_stride,
+                       const int64_t* slot_mapping, int64_t num_tokens,
+                       int32_t num_heads, int32_t num_kv_heads, int32_t head_dim,
+                       int32_t dtype, int32_t block_size, int64_t num_slots,
+                       int64_t max_position, void* stream);
+
+/*
  * Copy-on-write block copy — replaces
  *   copy_blocks               runtime/worker/llm_worker/ops/cache_ops.py:8-36
  *   copy_blocks_kernel        runtime/worker/llm_worker/ops/triton/cache_kernels.py:5-36

@@ -388,6 +388,11 @@ int lms_check_device_errors(void* stream, int64_t* index, int64_t* value) {
   LMS_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
   if (index) *index = h.index;
   if (value) *value = h.value;
+  if (h.code == kErrBadPosition) {
+    snprintf(g_cuda_msg, sizeof(g_cuda_msg), "position %lld of token %lld is outside the cos/sin cache",
+             h.value, h.index);
+    return LMS_ERR_INDEX;
+  }
   if (h.code == kErrWaitTimeout) {
     snprintf(g_cuda_msg, sizeof(g_cuda_msg),
              "kernel %u gave up waiting for a bulk copy (task %lld)", h.where,
@@ -490,6 +495,75 @@ int lms_append_paged_kv_cache(const void* key, const void* value,
                       cache_layer_stride, block_stride, slot_stride, nullptr, 0,
                       num_tokens, num_layers, row_bytes, block_size,
                       num_blocks * (int64_t)block_size, stream, &paged);
+}
+
+int lms_rope_and_cache(const void* query, const void* key, const void* value,
+                       int64_t query_token_stride, int64_t key_token_stride,
+                       int64_t value_token_stride, const void* positions,
+                       int32_t positions_are_int64, const void* cos_sin_cache,
+                       int64_t cos_sin_row_stride, void* q_out,
+                       int64_t q_out_token_stride, void* k_out,
+                       int64_t k_out_token_stride, void* key_cache,
+                       void* value_cache, int64_t block_stride, int64_t slot_stride,
+                       const int64_t* slot_mapping, int64_t num_tokens,
+                       int32_t num_heads, int32_t num_kv_heads, int32_t head_dim,
+                       int32_t dtype, int32_t block_size, int64_t num_slots,
+                       int64_t max_position, void* stream) {
+  if (num_tokens < 0 || num_tokens > 0x7fffffffll || num_heads <= 0 || num_kv_heads <= 0 ||
+      head_dim <= 0 || num_slots < 0 || max_position < 0 || (dtype != 0 && dtype != 1))
+    return LMS_ERR_RANGE;
+  if (head_dim % 16 != 0) return LMS_ERR_UNSUPPORTED;
+  if (num_tokens == 0) return LMS_OK;
+  const bool cached = key_cache != nullptr || value_cache != nullptr;
+  if (!query || !key || !positions || !cos_sin_cache || !q_out) return LMS_ERR_NULL;
+  if (cached && (!key_cache || !value_cache || !value || !slot_mapping)) return LMS_ERR_NULL;
+  if (cached && block_size <= 0) return LMS_ERR_RANGE;
+  if (!ptr16(query) || !ptr16(key) || !ptr16(cos_sin_cache) || !ptr16(q_out) || !ptr16(k_out) ||
+      !mult16(query_token_stride) || !mult16(key_token_stride) ||
+      !mult16(cos_sin_row_stride) || !mult16(q_out_token_stride) ||
+      !mult16(k_out_token_stride) ||
+      ((uintptr_t)positions & (positions_are_int64 ? 7u : 3u)) != 0)
+    return LMS_ERR_ALIGN;
+  if (cached && (!ptr16(value) || !ptr16(key_cache) || !ptr16(value_cache) ||
+                 !mult16(value_token_stride) || !mult16(block_stride) ||
+                 !mult16(slot_stride) || ((uintptr_t)slot_mapping & 7u) != 0))
+    return LMS_ERR_ALIGN;
+
+  DeviceState* ds = nullptr;
+  if (int rc = device_state(&ds)) return rc;
+  RopeParams p{};
+  p.q = (const char*)query;
+  p.k = (const char*)key;
+  p.v = (const char*)value;
+  p.q_tok = query_token_stride;
+  p.k_tok = key_token_stride;
+  p.v_tok = value_token_stride;
+  p.positions = positions;
+  p.pos64 = positions_are_int64 ? 1 : 0;
+  p.cos_sin = (const char*)cos_sin_cache;
+  p.cs_row = cos_sin_row_stride;
+  p.q_out = (char*)q_out;
+  p.qo_tok = q_out_token_stride;
+  p.k_out = (char*)k_out;
+  p.ko_tok = k_out_token_stride;
+  p.kcache = cached ? (char*)key_cache : nullptr;
+  p.vcache = cached ? (char*)value_cache : nullptr;
+  p.block_stride = block_stride;
+  p.slot_stride = slot_stride;
+  p.slots = (const long long*)slot_mapping;
+  p.num_slots = num_slots;
+  p.max_pos = max_position;
+  p.num_tokens = (int)num_tokens;
+  p.num_heads = num_heads;
+  p.num_kv_heads = num_kv_heads;
+  p.head_dim = head_dim;
+  p.block_size = cached ? block_size : 1;
+  p.is_bf16 = dtype;
+  p.err = ds->err;
+  p.checks = g_checks.load(std::memory_order_relaxed);
+  LMS_CUDA(launch_rope_cache(p, (cudaStream_t)stream));
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return LMS_OK;
 }
 
 int lms_copy_blocks(void* kv, int64_t layer_stride, int64_t block_stride,

@@ -17,6 +17,7 @@ enum : unsigned int {
   kWhereSwapOut = 3,
   kWhereSwapIn = 4,
   kWhereTransfer = 5,
+  kWhereRope = 6,
 };
 
 // ------------------------------------------------------------ paged cache write
@@ -83,5 +84,33 @@ struct CopyParams {
 // destinations streamed (fan-out copies).
 cudaError_t launch_chunk_copy(const CopyParams& p, int variant, int policy,
                               int grid_ctas, cudaStream_t stream);
+
+// ------------------------------------------------------------ rotary embedding + cache write
+struct RopeParams {
+  const char* q;
+  const char* k;
+  const char* v;          // unused when there is no cache
+  long long q_tok, k_tok, v_tok;  // bytes between consecutive tokens
+  const void* positions;  // int32 or int64 [T]
+  int pos64;
+  const char* cos_sin;    // [max_pos, 2 * head_dim] elements: cos row then sin row
+  long long cs_row;       // bytes between consecutive positions
+  char* q_out;
+  long long qo_tok;
+  char* k_out;            // optional rotated-K output, nullptr to skip
+  long long ko_tok;
+  char* kcache;           // nullptr (with vcache) = rotary embedding only
+  char* vcache;
+  long long block_stride, slot_stride;
+  const long long* slots;
+  long long num_slots, max_pos;  // debug-check bounds (0 = unchecked)
+  int num_tokens, num_heads, num_kv_heads, head_dim;
+  int block_size, block_shift;
+  int is_bf16;
+  ErrRecord* err;
+  int checks;
+};
+
+cudaError_t launch_rope_cache(const RopeParams& p, cudaStream_t stream);
 
 }  // namespace lms

@@ -28,6 +28,7 @@ enum : unsigned int {
   kErrBadSrcBlock = 2,
   kErrBadDstBlock = 3,
   kErrWaitTimeout = 4,
+  kErrBadPosition = 5,
 };
 
 __device__ __forceinline__ void report(ErrRecord* e, unsigned int code,

@@ -25,20 +25,38 @@ def available() -> bool:
     return (reference_root() / KERNEL_FILE).exists()
 
 
-_module = None
+ROPE_KERNEL_FILE = "runtime/worker/llm_worker/ops/triton/rotary_embedding.py"
+_modules = {}
+
+
+def _load(rel_path: str):
+    if rel_path not in _modules:
+        if os.environ.get("TRITON_INTERPRET") != "1":
+            raise RuntimeError("set TRITON_INTERPRET=1 before triton is first imported")
+        spec = importlib.util.spec_from_file_location(
+            "lmserve_ref_" + Path(rel_path).stem, reference_root() / rel_path)
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        _modules[rel_path] = mod
+    return _modules[rel_path]
 
 
 def _kernels():
-    global _module
-    if _module is None:
-        if os.environ.get("TRITON_INTERPRET") != "1":
-            raise RuntimeError("set TRITON_INTERPRET=1 before triton is first imported")
-        spec = importlib.util.spec_from_file_location("lmserve_ref_cache_kernels",
-                                                      reference_root() / KERNEL_FILE)
-        mod = importlib.util.module_from_spec(spec)
-        spec.loader.exec_module(mod)
-        _module = mod
-    return _module
+    return _load(KERNEL_FILE)
+
+
+def rotary_pos_emb(query, key, positions, cos_sin_cache, head_dim):
+    """``rotary_pos_emb`` of ``ops/rotary_embedding_ops.py:8-38`` (same launch arguments)."""
+    import torch
+    num_tokens = positions.shape[0]
+    num_heads = query.shape[1] // head_dim
+    num_kv_heads = key.shape[1] // head_dim
+    rotary_dim = cos_sin_cache.shape[-1] // 2
+    q_out, k_out = torch.empty_like(query), torch.empty_like(key)
+    _load(ROPE_KERNEL_FILE).apply_rotary_pos_emb_kernel[(num_tokens,)](
+        query, key, positions, cos_sin_cache, q_out, k_out, num_tokens, num_heads,
+        num_kv_heads, head_dim, rotary_dim, BLOCK_SIZE=rotary_dim // 2)
+    return q_out, k_out
 
 
 def copy_blocks(kv_caches, pairs) -> None:

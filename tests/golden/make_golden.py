@@ -92,6 +92,21 @@ def plumbing_digests():
     (HERE / "plumbing_llama32_1b.json").write_text(json.dumps(out, indent=1) + "\n")
 
 
+def rope_case(name, seed, T, NH, NKV, HD, max_pos=512):
+    """fp16 only: the interpreter evaluates bf16 arithmetic to NaN."""
+    from oracle import rope_oracle
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(T, NH * HD, generator=g).to(torch.float16)
+    k = torch.randn(T, NKV * HD, generator=g).to(torch.float16)
+    pos = torch.randint(0, max_pos, (T,), generator=g, dtype=torch.int32)
+    cs = rope_oracle.build_cos_sin_cache(max_pos, HD, torch.float16)
+    qo, ko = triton_ref.rotary_pos_emb(q, k, pos, cs, HD)
+    np.savez_compressed(HERE / f"{name}.npz", head_dim=HD, query=tensor_to_words(q),
+                        key=tensor_to_words(k), positions=pos.numpy(),
+                        cos_sin_cache=tensor_to_words(cs), q_out=tensor_to_words(qo),
+                        k_out=tensor_to_words(ko))
+
+
 def main():
     if not triton_ref.available():
         raise SystemExit("LMServe source tree not found; set LMSERVE_SRC")
@@ -101,6 +116,8 @@ def main():
     small_copy("copy_fp16_fanout", 21, "fp16", 2, 16, 4, 2, 8,
                [(1, 9), (1, 10), (1, 15), (3, 0), (7, 12)])
     small_copy("copy_bf16_l3", 22, "bf16", 3, 12, 16, 1, 16, [(0, 11), (5, 6), (5, 7), (2, 1)])
+    rope_case("rope_fp16_llama", 31, 6, 4, 2, 128)
+    rope_case("rope_fp16_d64", 32, 9, 3, 1, 64, max_pos=64)
     plumbing_digests()
     print("golden vectors written to", HERE)
 
