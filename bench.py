@@ -310,6 +310,8 @@ def run_ours(args):
             ops.update(bench_prefill_cow(comm, stream, cache_view, dev, peak_gbs, sampler, args.small))
         if world == 1 and ops_wanted & {"all", "swap"}:
             ops.update(bench_swap(comm, stream, cache_view, dev, args, sampler))
+        if world == 1 and ops_wanted & {"all", "rope"}:
+            ops.update(bench_rope_fusion(comm, stream, cache_view, dev, args, sampler))
         if ops_wanted & {"all", "tp8"}:
             ops.update(bench_tp8_decode(comm, stream, cache_view, dev, rank, world, peak_gbs, args, sampler))
         if world >= 2 and world % 2 == 0 and ops_wanted & {"all", "transfer"}:
@@ -486,6 +488,66 @@ def bench_swap(comm, stream, cache_view, dev, args, sampler):
                             "moved_blocks": n_blocks, "pin_seconds": pin_s}
     finally:
         pool.close()
+    return out
+
+
+def bench_rope_fusion(comm, stream, cache_view, dev, args, sampler):
+    """One decode layer of Llama-3.1-8B (256 tokens, 32 query / 8 KV heads of 128): rotary
+    embedding then cache write as two launches, against the fused launch.  32 layers per CUDA
+    graph, rotating input sets."""
+    from lmserve_b200.ops import cache_ops, rotary_embedding_ops as R
+    from oracle.rope_oracle import build_cos_sin_cache
+    s = W.SHAPES["llama31_8b"]
+    if args.small:
+        s = s.scaled(num_blocks=2048)
+    kv = cache_view(s)
+    T, NH, NKV, HD = 256, 32, 8, 128
+    cs = build_cos_sin_cache(8192, HD, torch.bfloat16).to(dev)
+    sets = []
+    for i in range(ROTATE):
+        w = W.config2(seed=3002 + 17 * i)
+        slots = w.slot_mapping
+        if args.small:
+            slots = renumber_blocks(slots, s.block_size, s.num_blocks, 177 + i)
+        qkv = torch.randn(s.num_layers, T, (NH + 2 * NKV) * HD, device=dev, dtype=torch.bfloat16)
+        pos = torch.from_numpy(w.context_lens.astype(np.int32)).to(dev)
+        sets.append((qkv, pos, torch.from_numpy(slots).to(dev)))
+    q_out = torch.empty(T, NH * HD, device=dev, dtype=torch.bfloat16)
+    k_out = torch.empty(T, NKV * HD, device=dev, dtype=torch.bfloat16)
+
+    def split(qkv_l):
+        return qkv_l[:, :NH * HD], qkv_l[:, NH * HD:(NH + NKV) * HD], qkv_l[:, (NH + NKV) * HD:]
+
+    def separate(j):
+        qkv, pos, slots = sets[j]
+        for l in range(s.num_layers):
+            q, k, v = split(qkv[l])
+            R._launch(q, k, None, pos, cs, HD, q_out, k_out, None, None)
+            cache_ops.reshape_and_cache(k_out.view(T, NKV, HD), v.view(T, NKV, HD), kv[l], slots)
+
+    def fused(j):
+        qkv, pos, slots = sets[j]
+        for l in range(s.num_layers):
+            q, k, v = split(qkv[l])
+            R._launch(q, k, v, pos, cs, HD, q_out, None, kv[l], slots)
+
+    out = {}
+    for name, fn in (("rope_then_cache_write_2_launches", separate), ("rope_and_cache_fused_1_launch", fused)):
+        fn(0)
+        torch.cuda.synchronize()
+        graphs = []
+        side = torch.cuda.Stream()
+        side.wait_stream(stream)
+        for j in range(ROTATE):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                fn(j)
+            graphs.append(g)
+        stream.wait_stream(side)
+        torch.cuda.synchronize()
+        reps = max(8, args.steps // 4)
+        ms = timed(comm, stream, lambda i: graphs[i % ROTATE].replay(), reps, 3, sampler) / reps
+        out[name] = {"us_per_layer": ms * 1e3 / s.num_layers, "us_per_32_layers": ms * 1e3}
     return out
 
 
