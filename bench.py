@@ -484,6 +484,20 @@ def bench_swap(comm, stream, cache_view, dev, args, sampler):
                           "pcie_peak_GB/s_measured_memcpy": peaks["h2d"],
                           "frac_of_pcie_peak": nbytes / (ms_in * 1e-3) / 1e9 / peaks["h2d"],
                           "round_trip_bit_exact": ok}
+        # layer-pipelined form: one launch per layer, each gated on / signalling a per-layer
+        # event, the way the KV worker and the model hand layers to each other
+        from lmserve_b200.kv_worker import KVWorker
+        worker = KVWorker.__new__(KVWorker)
+        worker.gpu_kv_caches, worker.device, worker.host_pool = kv, dev, pool
+        worker.num_layers = s.num_layers
+        post = [torch.cuda.Event() for _ in range(s.num_layers)]
+        for e in post:
+            e.record(stream)
+        pre = [torch.cuda.Event() for _ in range(s.num_layers)]
+        ms_lo = timed(comm, stream, lambda i: worker._swap([w.out_pairs], "out", stream, None, post, 1), 1, 1, sampler)
+        ms_li = timed(comm, stream, lambda i: worker._swap([w.in_pairs], "in", stream, pre, None, 1), 1, 1, sampler)
+        out["swap_per_layer_launches"] = {"launches": s.num_layers, "out_GB/s": nbytes / (ms_lo * 1e-3) / 1e9,
+                                          "in_GB/s": nbytes / (ms_li * 1e-3) / 1e9}
         out["swap_pool"] = {"host_blocks": nhb, "host_pool_GiB": pool.nbytes / (1 << 30),
                             "moved_blocks": n_blocks, "pin_seconds": pin_s}
     finally:

@@ -25,7 +25,9 @@ constexpr int kMaxDevices = 64;
 
 struct DeviceState {
   int sms = 0;
-  ErrRecord* err = nullptr;  // device memory, allocated on first use
+  // Device memory, allocated on first use.  Published with release order after `sms` is
+  // set, read with acquire order, so a thread that sees the pointer sees the whole state.
+  std::atomic<ErrRecord*> err{nullptr};
   // Device copy of the most recent host-side pair table (the *_host entry points).
   long long* table = nullptr;
   long long table_cap = 0;        // capacity in pairs
@@ -59,14 +61,18 @@ int device_state(DeviceState** out) {
   LMS_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= kMaxDevices) return LMS_ERR_RANGE;
   DeviceState& s = g_dev[dev];
-  if (s.err == nullptr) {
+  if (s.err.load(std::memory_order_acquire) == nullptr) {
     std::lock_guard<std::mutex> lock(g_mutex);
-    if (s.err == nullptr) {
+    if (s.err.load(std::memory_order_relaxed) == nullptr) {
       LMS_CUDA(cudaDeviceGetAttribute(&s.sms, cudaDevAttrMultiProcessorCount, dev));
       ErrRecord* e = nullptr;
       LMS_CUDA(cudaMalloc(&e, sizeof(ErrRecord)));
-      LMS_CUDA(cudaMemset(e, 0, sizeof(ErrRecord)));
-      s.err = e;
+      cudaError_t me = cudaMemset(e, 0, sizeof(ErrRecord));
+      if (me != cudaSuccess) {
+        cudaFree(e);
+        return cuda_fail(me, "cudaMemset(error record)");
+      }
+      s.err.store(e, std::memory_order_release);
     }
   }
   *out = &s;
@@ -81,7 +87,7 @@ int tuned(int key, int fallback) {
   return v > 0 ? v : fallback;
 }
 int tuned_variant(int key, int fallback) {
-  // variants are 0..2; stored +1 so that 0 means "not set"
+  // variant numbers start at 0, so they are stored +1 and 0 means "not set"
   const int v = g_tuning[key].load(std::memory_order_relaxed);
   return v > 0 ? v - 1 : fallback;
 }
@@ -163,7 +169,7 @@ int write_params(const void* key, const void* value, int64_t key_tok,
 int write_launch(WriteParams p, void* stream) {
   DeviceState* ds = nullptr;
   if (int rc = device_state(&ds)) return rc;
-  p.err = ds->err;
+  p.err = ds->err.load(std::memory_order_relaxed);
   p.checks = g_checks.load(std::memory_order_relaxed);
   const int variant = tuned_variant(LMS_TUNE_WRITE_VARIANT, -1);  // -1: launch_write chooses
   const int tile = tuned(LMS_TUNE_WRITE_TILE_BYTES, 0);
@@ -224,7 +230,7 @@ int chunk_copy(const void* src, int64_t src_layer, int64_t src_block, void* dst,
   p.num_layers = num_layers;
   p.layer_major = layer_major;
   p.chunk_bytes = (int)chunk_bytes;
-  p.err = ds->err;
+  p.err = ds->err.load(std::memory_order_relaxed);
   p.where = where;
   p.checks = g_checks.load(std::memory_order_relaxed);
 
@@ -380,11 +386,11 @@ int lms_check_device_errors(void* stream, int64_t* index, int64_t* value) {
   DeviceState* ds = nullptr;
   if (int rc = device_state(&ds)) return rc;
   ErrRecord h{};
-  LMS_CUDA(cudaMemcpyAsync(&h, ds->err, sizeof(h), cudaMemcpyDeviceToHost,
+  LMS_CUDA(cudaMemcpyAsync(&h, ds->err.load(std::memory_order_relaxed), sizeof(h), cudaMemcpyDeviceToHost,
                            (cudaStream_t)stream));
   LMS_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
   if (h.code == kErrNone) return LMS_OK;
-  LMS_CUDA(cudaMemsetAsync(ds->err, 0, sizeof(h), (cudaStream_t)stream));
+  LMS_CUDA(cudaMemsetAsync(ds->err.load(std::memory_order_relaxed), 0, sizeof(h), (cudaStream_t)stream));
   LMS_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
   if (index) *index = h.index;
   if (value) *value = h.value;
@@ -559,7 +565,7 @@ int lms_rope_and_cache(const void* query, const void* key, const void* value,
   p.head_dim = head_dim;
   p.block_size = cached ? block_size : 1;
   p.is_bf16 = dtype;
-  p.err = ds->err;
+  p.err = ds->err.load(std::memory_order_relaxed);
   p.checks = g_checks.load(std::memory_order_relaxed);
   LMS_CUDA(launch_rope_cache(p, (cudaStream_t)stream));
   g_launches.fetch_add(1, std::memory_order_relaxed);

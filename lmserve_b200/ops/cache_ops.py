@@ -196,10 +196,7 @@ def reshape_and_cache(
     ``slot = block_table[pos // block_size] * block_size + pos % block_size``.
     Entries ``< 0`` are skipped.
     """
-    _write_layers(key.unsqueeze(0) if key.dim() == 3 else key,
-                  value.unsqueeze(0) if value.dim() == 3 else value,
-                  kv_cache.unsqueeze(0) if kv_cache.dim() == 5 else kv_cache,
-                  slot_mapping)
+    _write_layers(key, value, kv_cache, slot_mapping)
 
 
 def reshape_and_cache_layers(
@@ -310,38 +307,68 @@ def append_paged_kv_cache(
 
 
 def _prepare_write(key, value, kv_caches, slot_mapping):
-    """Validates a multi-layer write and returns (device, keepalive, argument tuple without the
-    stream) for ``lms_reshape_and_cache_layers``."""
-    for n, t in (("key", key), ("value", value), ("kv_caches", kv_caches)):
-        _require_cuda(n, t)
-    if key.dim() != 4 or value.dim() != 4 or key.shape != value.shape:
+    """Validates a write and returns (device, keepalive, argument tuple without the stream) for
+    ``lms_reshape_and_cache_layers``.  ``key``/``value`` ``[L, T, H, D]`` with the 6-D cache, or
+    ``[T, H, D]`` with one layer's 5-D cache.  Runs once per layer per step when the caller
+    does not plan: only attribute reads, no tensor indexing."""
+    kshape, cshape = key.shape, kv_caches.shape
+    layered = len(kshape) == 4
+    if layered:
+        if len(cshape) != 6 or cshape[2] != 2:
+            raise ValueError("kv cache must be [L, num_blocks, 2, block_size, H, D]")
+        L, NB, _, BS, H, D = cshape
+        cst = kv_caches.stride()
+        c_layer, c_block, c_in = cst[0], cst[1], cst[2:]
+        if kshape[0] != L:
+            raise ValueError(f"key {tuple(kshape)} does not match cache {tuple(cshape)}")
+        kst, vst = key.stride(), value.stride()
+        k_layer, v_layer, kst, vst = kst[0], vst[0], kst[1:], vst[1:]
+        T = kshape[1]
+        row_shape = kshape[2:]
+    elif len(kshape) == 3:
+        if len(cshape) != 5 or cshape[1] != 2:
+            raise ValueError("a layer's kv cache must be [num_blocks, 2, block_size, H, D]")
+        NB, _, BS, H, D = cshape
+        L = 1
+        cst = kv_caches.stride()
+        c_layer, c_block, c_in = 0, cst[0], cst[1:]
+        kst, vst = key.stride(), value.stride()
+        k_layer = v_layer = 0
+        T = kshape[0]
+        row_shape = kshape[1:]
+    else:
         raise ValueError("key and value must both be [L, T, H, D] (or [T, H, D] for one layer)")
-    if kv_caches.dim() != 6 or kv_caches.shape[2] != 2:
-        raise ValueError("kv cache must be [L, num_blocks, 2, block_size, H, D]")
-    L, NB, _, BS, H, D = kv_caches.shape
-    if key.shape[0] != L or tuple(key.shape[2:]) != (H, D):
-        raise ValueError(f"key {tuple(key.shape)} does not match cache {tuple(kv_caches.shape)}")
-    if key.dtype != kv_caches.dtype or value.dtype != kv_caches.dtype:
+    if value.shape != kshape:
+        raise ValueError("key and value must have the same shape")
+    if tuple(row_shape) != (H, D):
+        raise ValueError(f"key {tuple(kshape)} does not match cache {tuple(cshape)}")
+    if not kv_caches.is_cuda or not key.is_cuda or not value.is_cuda:
+        raise RuntimeError("key, value and the cache must live on a CUDA device; the cache ops have no CPU path")
+    cdtype = kv_caches.dtype
+    if key.dtype != cdtype or value.dtype != cdtype:
         raise TypeError("cache dtype must match key/value dtype (bytes are copied, not converted)")
-    es = kv_caches.element_size()
-    if NB > 0 and L > 0 and not kv_caches[0, 0].is_contiguous():
+    if NB > 0 and tuple(c_in) != (BS * H * D, H * D, D, 1):
         raise ValueError("each cache block [2, block_size, H, D] must be contiguous")
+    if T > 0 and (kst[2] != 1 or vst[2] != 1 or (H > 1 and (kst[1] != D or vst[1] != D))):
+        raise ValueError("each token's [H, D] row must be contiguous")
+    es = kv_caches.element_size()
     dev = kv_caches.device
-    T = key.shape[1]
-    k_tok, row_bytes = _row_layout("key", key[0])
-    v_tok, _ = _row_layout("value", value[0])
-    slots = _slots_i64(slot_mapping, dev)
-    if slots.dim() == 1 and slots.shape[0] == T:
+    row_bytes = H * D * es
+    slots = slot_mapping
+    if slots.dtype != torch.int64 or slots.device != dev or not slots.is_contiguous():
+        slots = _slots_i64(slot_mapping, dev)
+    sshape = slots.shape
+    if len(sshape) == 1 and sshape[0] == T:
         slot_layer = 0
-    elif slots.dim() == 2 and tuple(slots.shape) == (L, T):
+    elif len(sshape) == 2 and tuple(sshape) == (L, T):
         slot_layer = T
     else:
-        raise ValueError(f"slot_mapping must be [T] or [L, T], got {tuple(slots.shape)}")
+        raise ValueError(f"slot_mapping must be [T] or [L, T], got {tuple(sshape)}")
     kbase = kv_caches.data_ptr()
-    args = (key.data_ptr(), value.data_ptr(), k_tok, v_tok,
-            key.stride(0) * es, value.stride(0) * es,
+    args = (key.data_ptr(), value.data_ptr(), kst[0] * es, vst[0] * es,
+            k_layer * es, v_layer * es,
             kbase, kbase + BS * row_bytes,
-            kv_caches.stride(0) * es, kv_caches.stride(1) * es, row_bytes,
+            c_layer * es, c_block * es, row_bytes,
             slots.data_ptr(), slot_layer, T, L, row_bytes, BS, NB * BS)
     return dev, (key, value, kv_caches, slots), args
 
@@ -349,7 +376,9 @@ def _prepare_write(key, value, kv_caches, slot_mapping):
 def _write_layers(key, value, kv_caches, slot_mapping) -> None:
     dev, _keep, args = _prepare_write(key, value, kv_caches, slot_mapping)
     with _OnDevice(dev):
-        _lib.check(_lib.lib().lms_reshape_and_cache_layers(*args, _stream_ptr(dev)))
+        rc = _lib.lib().lms_reshape_and_cache_layers(*args, _stream_ptr(dev))
+    if rc:
+        _lib.check(rc)
 
 
 class WritePlan:
@@ -366,8 +395,6 @@ class WritePlan:
 
     def __init__(self, key: torch.Tensor, value: torch.Tensor, kv_cache: torch.Tensor,
                  slot_mapping: torch.Tensor):
-        if key.dim() == 3:
-            key, value, kv_cache = key.unsqueeze(0), value.unsqueeze(0), kv_cache.unsqueeze(0)
         self.device, self._keep, args = _prepare_write(key, value, kv_cache, slot_mapping)
         handle = ctypes.c_void_p()
         with torch.cuda.device(self.device):
