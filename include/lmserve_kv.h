@@ -383,6 +383,16 @@ int lms_ipc_open(const void* handle64, int64_t offset, void** device_ptr);
 int lms_ipc_close(void* device_ptr, int64_t offset);
 
 /*
+ * Self-test of the bounded device-side wait used by the bulk-copy (TMA) kernel variants: one
+ * warp waits on a shared-memory barrier that nothing ever completes, gives up after
+ * `limit_us` microseconds, records the time-out in the device error record and returns.  The
+ * kernel neither traps nor spins forever, and the context stays usable;
+ * lms_check_device_errors afterwards returns LMS_ERR_CUDA with a "gave up waiting" message.
+ * `limit_us` is clamped to [1, 1000000].  No counterpart in the reference.
+ */
+int lms_selftest_bounded_wait(int64_t limit_us, void* stream);
+
+/*
  * Plain cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDefault) on `stream`: the copy-engine
  * baseline the swap and transfer kernels are measured against (one contiguous DMA).  No
  * counterpart in the reference, which issues its copies through pycuda

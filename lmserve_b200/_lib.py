@@ -94,6 +94,7 @@ SIGNATURES = {
     "lms_ipc_export": (c_int, [c_void_p, c_void_p, POINTER(c_int64)]),
     "lms_ipc_open": (c_int, [c_void_p, c_int64, POINTER(c_void_p)]),
     "lms_ipc_close": (c_int, [c_void_p, c_int64]),
+    "lms_selftest_bounded_wait": (c_int, [c_int64, c_void_p]),
     "lms_memcpy_async": (c_int, [c_void_p, c_void_p, c_int64, c_void_p]),
     "lms_launch_count": (c_int64, []),
 }

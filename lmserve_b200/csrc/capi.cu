@@ -45,6 +45,9 @@ thread_local char g_cuda_msg[256] = "";
 int cuda_fail(cudaError_t e, const char* what) {
   snprintf(g_cuda_msg, sizeof(g_cuda_msg), "%s: %s (%s)", what,
            cudaGetErrorName(e), cudaGetErrorString(e));
+  // The runtime also remembers the error as the thread's "last error"; clear it so that the
+  // cudaGetLastError() after a later, healthy kernel launch does not report this one again.
+  cudaGetLastError();
   return LMS_ERR_CUDA;
 }
 
@@ -802,6 +805,17 @@ int lms_ipc_open(const void* handle64, int64_t offset, void** device_ptr) {
 int lms_ipc_close(void* device_ptr, int64_t offset) {
   if (!device_ptr) return LMS_OK;
   LMS_CUDA(cudaIpcCloseMemHandle((char*)device_ptr - offset));
+  return LMS_OK;
+}
+
+int lms_selftest_bounded_wait(int64_t limit_us, void* stream) {
+  DeviceState* ds = nullptr;
+  if (int rc = device_state(&ds)) return rc;
+  if (limit_us < 1) limit_us = 1;
+  if (limit_us > 1000000) limit_us = 1000000;
+  LMS_CUDA(launch_wait_selftest(ds->err.load(std::memory_order_relaxed),
+                                (unsigned long long)limit_us * 1000ull, (cudaStream_t)stream));
+  g_launches.fetch_add(1, std::memory_order_relaxed);
   return LMS_OK;
 }
 

@@ -222,6 +222,20 @@ chunk_copy_bulk(const CopyParams p) {
   bulk_wait_all();
 }
 
+// The wait of the bulk kernels, exercised on a barrier nobody completes.
+__global__ void __launch_bounds__(32) wait_selftest_kernel(ErrRecord* err,
+                                                          unsigned long long limit_ns) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    mbar_fence_init();
+  }
+  __syncwarp();
+  const bool ok = mbar_wait_bounded(&bar, 0, limit_ns);
+  if (__any_sync(0xffffffffu, !ok) && threadIdx.x == 0)
+    report(err, kErrWaitTimeout, kWhereSelfTest, 0, (long long)limit_ns);
+}
+
 template <class Vec, int POLICY>
 cudaError_t launch_vec(CopyParams p, int grid_ctas, cudaStream_t stream) {
   constexpr int THREADS = 256;
@@ -254,6 +268,12 @@ cudaError_t launch_direct(const CopyParams& p, cudaStream_t stream) {
 }
 
 }  // namespace
+
+cudaError_t launch_wait_selftest(ErrRecord* err, unsigned long long limit_ns,
+                                 cudaStream_t stream) {
+  wait_selftest_kernel<<<1, 32, 0, stream>>>(err, limit_ns);
+  return cudaGetLastError();
+}
 
 cudaError_t launch_chunk_copy(const CopyParams& p_in, int variant, int policy,
                               int grid_ctas, cudaStream_t stream) {

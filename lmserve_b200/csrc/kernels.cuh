@@ -18,6 +18,7 @@ enum : unsigned int {
   kWhereSwapIn = 4,
   kWhereTransfer = 5,
   kWhereRope = 6,
+  kWhereSelfTest = 7,
 };
 
 // ------------------------------------------------------------ paged cache write
@@ -112,5 +113,8 @@ struct RopeParams {
 };
 
 cudaError_t launch_rope_cache(const RopeParams& p, cudaStream_t stream);
+
+// One warp waits (bounded) on an mbarrier that is never completed; see lms_selftest_bounded_wait.
+cudaError_t launch_wait_selftest(ErrRecord* err, unsigned long long limit_ns, cudaStream_t stream);
 
 }  // namespace lms

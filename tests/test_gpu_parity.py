@@ -464,3 +464,35 @@ def test_append_paged_kv_cache_matches_flashinfer():
     torch.cuda.synchronize()
     assert torch.equal(ours.view(torch.int16), theirs.view(torch.int16))
     assert not np.array_equal(to_words(ours), cache)
+
+
+# ----------------------------------------------------------------- failure handling
+def test_bounded_wait_times_out_and_the_context_survives():
+    """A device-side wait that nothing satisfies gives up after its limit, reports through the
+    error record, and the next kernels run normally."""
+    import time
+    L = _lib.lib()
+    assert L.lms_check_device_errors(None, None, None) == 0
+    t0 = time.perf_counter()
+    assert L.lms_selftest_bounded_wait(20000, None) == 0        # 20 ms limit
+    rc = L.lms_check_device_errors(None, None, None)
+    waited = time.perf_counter() - t0
+    assert rc == _lib.LMS_ERR_CUDA
+    assert b"gave up waiting" in L.lms_last_cuda_error()
+    assert 0.015 < waited < 2.0
+    assert L.lms_check_device_errors(None, None, None) == 0     # record cleared
+    g = load_npz("fill_fp16_t8")
+    kc, vc = to_tensor(g["key_cache_in"], "fp16", DEV), to_tensor(g["value_cache_in"], "fp16", DEV)
+    cache_ops.fill_key_cache(to_tensor(g["key"], "fp16", DEV), to_tensor(g["value"], "fp16", DEV),
+                             kc, vc, torch.from_numpy(g["slot_mapping"]).to(DEV))
+    torch.cuda.synchronize()
+    assert np.array_equal(to_words(kc), g["key_cache_out"])
+
+
+def test_peer_enable_errors_are_statuses():
+    L = _lib.lib()
+    assert L.lms_peer_enable(torch.cuda.current_device()) == 0   # self: nothing to enable
+    rc = L.lms_peer_enable(4096)                                 # no such device
+    assert rc in (_lib.LMS_ERR_CUDA, _lib.LMS_ERR_PEER)
+    x = torch.ones(8, device=DEV)                                # context still fine
+    assert float(x.sum()) == 8.0
