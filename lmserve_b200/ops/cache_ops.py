@@ -92,15 +92,8 @@ def flatten_block_map(src_to_dst: Union[Dict[int, Iterable[int]], PairList]) -> 
     ``BlockMapping.entries`` (``proto/worker.proto:78-86``).
     """
     if isinstance(src_to_dst, dict):
-        n = sum(len(v) for v in src_to_dst.values())
-        out = np.empty((n, 2), dtype=np.int64)
-        i = 0
-        for src, dsts in src_to_dst.items():
-            k = len(dsts)
-            out[i:i + k, 0] = src
-            out[i:i + k, 1] = np.asarray(dsts, dtype=np.int64) if k else 0
-            i += k
-        return out
+        flat = [x for src, dsts in src_to_dst.items() for dst in dsts for x in (src, dst)]
+        return np.array(flat, dtype=np.int64).reshape(-1, 2)
     if isinstance(src_to_dst, torch.Tensor):
         arr = src_to_dst.detach().cpu().numpy()
     else:
@@ -424,15 +417,19 @@ class WritePlan:
 
 # --------------------------------------------------------------------- copies
 def _cache_geometry(kv_caches: torch.Tensor) -> Tuple[int, int, int, int, int]:
-    """(num_layers, num_blocks, layer stride, block stride, chunk bytes) of a layer-major cache."""
-    if kv_caches.dim() < 3:
+    """(num_layers, num_blocks, layer stride, block stride, chunk bytes) of a layer-major cache
+    ``[L, NB, ...]`` whose (layer, block) chunks are contiguous.  Attribute reads only."""
+    shape = kv_caches.shape
+    if len(shape) < 3:
         raise ValueError("kv_caches must be [num_layers, num_blocks, ...]")
-    L, NB = kv_caches.shape[0], kv_caches.shape[1]
+    strides = kv_caches.stride()
     es = kv_caches.element_size()
-    chunk = kv_caches[0, 0].numel() * es
-    if not kv_caches[0, 0].is_contiguous():
-        raise ValueError("each (layer, block) chunk of the cache must be contiguous")
-    return L, NB, kv_caches.stride(0) * es, kv_caches.stride(1) * es, chunk
+    chunk_elems = 1
+    for dim in range(len(shape) - 1, 1, -1):
+        if shape[dim] != 1 and strides[dim] != chunk_elems:
+            raise ValueError("each (layer, block) chunk of the cache must be contiguous")
+        chunk_elems *= shape[dim]
+    return shape[0], shape[1], strides[0] * es, strides[1] * es, chunk_elems * es
 
 
 def copy_blocks(
@@ -531,6 +528,7 @@ def transfer_blocks(
     src_kv_caches: torch.Tensor,
     dst_kv_caches,
     block_pairs: PairList,
+    layers: Optional[Tuple[int, int]] = None,
 ) -> None:
     """Pushes blocks of the local cache into a peer GPU's cache: ``dst[:, d] = src[:, s]``.
 
@@ -538,7 +536,9 @@ def transfer_blocks(
     kernel on the source GPU storing over NVLink.  ``dst_kv_caches`` is either a
     tensor on another device of this process (peer access is enabled on demand)
     or a :class:`lmserve_b200.kv_worker.PeerCache` opened from another
-    process's IPC handle.  Runs on the source device's current stream.
+    process's IPC handle.  Runs on the source device's current stream.  ``layers=(begin, end)``
+    pushes only that layer range, so a prefill worker can ship each layer as soon as it is
+    computed instead of waiting for the whole forward pass.
     """
     _require_cuda("src_kv_caches", src_kv_caches)
     dev = src_kv_caches.device
@@ -557,11 +557,15 @@ def transfer_blocks(
         dst_ptr = dst_kv_caches.device_ptr
     if dL != L or d_chunk != chunk:
         raise ValueError("source and destination caches must have the same layers and chunk size")
+    l0, l1 = (0, L) if layers is None else layers
+    if not (0 <= l0 <= l1 <= L):
+        raise ValueError(f"layer range {layers} outside [0, {L}]")
     on_device, _keep, ptr, n = _pair_table(block_pairs, dev)
-    if n == 0:
+    if n == 0 or l0 == l1:
         return
     L_ = _lib.lib()
     fn = L_.lms_transfer_blocks if on_device else L_.lms_transfer_blocks_host
     with _OnDevice(dev):
-        _lib.check(fn(src_kv_caches.data_ptr(), s_layer, s_block, dst_ptr, d_layer, d_block,
-                      chunk, L, ptr, n, NB, dNB, _stream_ptr(dev)))
+        _lib.check(fn(src_kv_caches.data_ptr() + l0 * s_layer, s_layer, s_block,
+                      dst_ptr + l0 * d_layer, d_layer, d_block,
+                      chunk, l1 - l0, ptr, n, NB, dNB, _stream_ptr(dev)))
