@@ -18,6 +18,33 @@ from .cache_ops import _OnDevice, _require_cuda, _slots_i64, _stream_ptr
 _DTYPE_CODE = {torch.float16: 0, torch.bfloat16: 1}
 
 
+def build_cos_sin_cache(max_position: int, head_dim: int, dtype: torch.dtype,
+                        base: float = 10000.0, rope_scaling: Optional[dict] = None,
+                        device=None) -> torch.Tensor:
+    """The ``[max_position, 2 * head_dim]`` table (cos row, then sin row, of ``cat(freqs,
+    freqs)``) that LMServe's ``RotaryEmbedding`` registers as ``cos_sin_cached``
+    (``models/layers/rotary_embedding.py:27-71``), including the Llama-3 frequency rescaling
+    when ``rope_scaling`` carries ``factor``, ``low_freq_factor``, ``high_freq_factor`` and
+    ``original_max_position_embeddings``.  Computed in fp32 and cast once, as there."""
+    import math
+    inv_freq = 1.0 / (base ** (torch.arange(0, head_dim, 2, dtype=torch.int64).float() / head_dim))
+    if rope_scaling is not None:
+        factor = rope_scaling["factor"]
+        low, high = rope_scaling["low_freq_factor"], rope_scaling["high_freq_factor"]
+        old_len = rope_scaling["original_max_position_embeddings"]
+        wavelen = 2 * math.pi / inv_freq
+        scaled = torch.where(wavelen > old_len / low, inv_freq / factor, inv_freq)
+        smooth = (old_len / wavelen - low) / (high - low)
+        blended = (1 - smooth) * inv_freq / factor + smooth * inv_freq
+        medium = ~(wavelen < old_len / high) & ~(wavelen > old_len / low)
+        inv_freq = torch.where(medium, blended, scaled)
+    t = torch.arange(max_position).float()
+    freqs = torch.einsum("i,j->ij", t, inv_freq.float())
+    emb = torch.cat((freqs, freqs), dim=-1)
+    table = torch.cat((emb.cos().to(dtype), emb.sin().to(dtype)), dim=-1)
+    return table if device is None else table.to(device)
+
+
 def _check_inputs(query, key, positions, cos_sin_cache, head_dim):
     for n, t in (("query", query), ("key", key), ("positions", positions),
                  ("cos_sin_cache", cos_sin_cache)):

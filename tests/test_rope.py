@@ -37,6 +37,22 @@ def test_oracle_matches_reference_kernel_fp16(name):
     assert torch.allclose(once.view_as(q), qo.float(), atol=4e-3, rtol=4e-3)
 
 
+def test_package_cos_sin_cache_matches_oracle_and_llama3_scaling():
+    from lmserve_b200.ops import build_cos_sin_cache
+    a = build_cos_sin_cache(128, 64, torch.bfloat16, base=500000.0)
+    b = rope_oracle.build_cos_sin_cache(128, 64, torch.bfloat16, base=500000.0)
+    assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+    scaling = {"factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+               "original_max_position_embeddings": 8192}
+    c = build_cos_sin_cache(64, 128, torch.float32, base=500000.0, rope_scaling=scaling)
+    plain = build_cos_sin_cache(64, 128, torch.float32, base=500000.0)
+    # high frequencies (short wavelengths) are untouched, the lowest frequency is divided by 8
+    assert torch.equal(c[:, 0], plain[:, 0])
+    inv_last = 1.0 / (500000.0 ** (126 / 128))
+    assert torch.allclose(c[5, 63], torch.cos(torch.tensor(5 * inv_last / 8.0)))
+    assert torch.allclose(c[5, 128 + 63], torch.sin(torch.tensor(5 * inv_last / 8.0)), atol=1e-7)
+
+
 def test_cos_sin_cache_layout():
     cs = rope_oracle.build_cos_sin_cache(16, 8, torch.float32)
     assert cs.shape == (16, 16)
