@@ -316,7 +316,7 @@ def run_ours(args):
 
         # ------------------------------------------------------------- other workloads
         if args.small:
-            ops_wanted = ops_wanted & {"prefill_cow"}
+            ops_wanted = ops_wanted & {"prefill_cow", "swap", "rope", "transfer_local"}
 
         def extra(names, fn):
             """Runs one of the other workloads; a failure there (a pool that does not fit, no
@@ -336,6 +336,9 @@ def run_ours(args):
                                                              sampler, args.small))
             extra(["swap"], lambda: bench_swap(comm, stream, cache_view, dev, args, sampler))
             extra(["rope"], lambda: bench_rope_fusion(comm, stream, cache_view, dev, args, sampler))
+            if torch.cuda.device_count() >= 2 and "transfer_local" in ops_wanted:
+                extra(["transfer_local"], lambda: bench_transfer_local(comm, stream, cache_view, dev,
+                                                                       args, sampler))
         extra(["tp8"], lambda: bench_tp8_decode(comm, stream, cache_view, dev, rank, world, peak_gbs,
                                                 args, sampler))
         if world >= 2 and world % 2 == 0:
@@ -463,8 +466,12 @@ def bench_swap(comm, stream, cache_view, dev, args, sampler):
     from lmserve_b200.ops import cache_ops
     s = W.SHAPES["llama31_8b_swap"]
     per_block = s.num_layers * s.chunk_bytes
-    nhb = host_pool_blocks(per_block, 131072, args.host_pool_gib)
-    n_blocks = min(8192, nhb)
+    if args.small:  # profiling case: 2048 GPU blocks (4 GiB), 1 GiB moved each way
+        s = s.scaled(num_blocks=2048)
+        nhb, n_blocks = 1024, 512
+    else:
+        nhb = host_pool_blocks(per_block, 131072, args.host_pool_gib)
+        n_blocks = min(8192, nhb)
     w = W.make_swap(s, nhb, n_blocks, seed=1004)
     kv = cache_view(s)
     out = {}
@@ -621,6 +628,26 @@ def bench_tp8_decode(comm, stream, cache_view, dev, rank, world, peak_gbs, args,
                                  "frac_of_hbm_peak": b / (ms * 1e-3) / 1e9 / peak_gbs}}
 
 
+def bench_transfer_local(comm, stream, cache_view, dev, args, sampler):
+    """The prefill->decode push between two GPUs of ONE process (peer access instead of CUDA
+    IPC): the case a single-process profiler can capture.  Llama-3.1-70B TP8 shard geometry;
+    4096 blocks x 80 layers x 8 KiB (512 blocks in the small profiling case)."""
+    from lmserve_b200.ops import cache_ops
+    s = W.SHAPES["llama31_70b_tp8"]
+    n_seqs = 4 if args.small else 32
+    if args.small:
+        s = s.scaled(num_blocks=4096)
+    src = cache_view(s)
+    dshape = s.scaled(num_blocks=8192)
+    dst = torch.empty(dshape.cache_shape, dtype=torch.bfloat16, device="cuda:1")
+    tr = W.make_transfer(s, n_seqs, 2048, seed=1105, dst_num_blocks=dshape.num_blocks)
+    pairs = torch.from_numpy(tr.pairs).to(dev)
+    reps = 3
+    ms = timed(comm, stream, lambda i: cache_ops.transfer_blocks(src, dst, pairs), reps, 2, sampler) / reps
+    torch.cuda.synchronize("cuda:1")
+    return {"transfer_local": {"ms": ms, "bytes": tr.bytes(), "GB/s": tr.bytes() / (ms * 1e-3) / 1e9}}
+
+
 def bench_transfer(comm, stream, cache_view, dev, rank, world, sampler):
     """Prefill GPU g pushes 32 x 2048-token sequences (4096 blocks x 80 layers x 8 KiB = 2.5 GiB)
     into random free blocks of decode GPU g + N/2 over NVLink."""
@@ -742,7 +769,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--ops", default="all",
-                    help="comma list of extra workloads: all, none, prefill_cow, swap, tp8, transfer")
+                    help="comma list of extra workloads: all, none, prefill_cow, swap, rope, tp8, "
+                         "transfer (multi-rank), transfer_local (two GPUs in one process; not in 'all')")
     ap.add_argument("--host-pool-gib", type=float, default=32.0,
                     help="cap of the pinned host pool of the swap workload")
     ap.add_argument("--no-cpu-baseline", action="store_true")
