@@ -22,7 +22,6 @@ between rank g and rank g + N/2.
 from __future__ import annotations
 
 import argparse
-import ctypes
 import json
 import os
 import statistics
@@ -148,7 +147,6 @@ def timed(comm: Comm, stream, fn, steps: int, warmup: int, sampler=None) -> floa
 # ----------------------------------------------------------------------------- our arm
 def run_ours(args):
     from lmserve_b200 import _lib
-    from lmserve_b200.kv_worker import HostPool
     from lmserve_b200.ops import cache_ops
 
     if not torch.cuda.is_available():

@@ -20,8 +20,6 @@ reference's own handler is unreachable (it reads a field the message does not ha
 from __future__ import annotations
 
 from concurrent import futures
-from typing import Optional
-
 import grpc
 from google.protobuf import descriptor_pb2, descriptor_pool, empty_pb2, message_factory
 

@@ -13,7 +13,7 @@ import ctypes
 import enum
 import pickle
 from dataclasses import dataclass, field
-from typing import Dict, List, Optional, Sequence, Tuple
+from typing import Dict, List, Optional, Sequence
 
 import numpy as np
 import torch
@@ -78,7 +78,7 @@ class HostPool:
     bf16 payloads are held as raw bytes, as the reference holds them as uint16.
     """
 
-    def __init__(self, num_blocks: int, num_layers: int, chunk_bytes: int):
+    def __init__(self, num_blocks: int, num_layers: int, chunk_bytes: int, _buffer=None):
         if num_blocks <= 0 or num_layers <= 0 or chunk_bytes <= 0 or chunk_bytes % 16:
             raise ValueError("host pool needs positive sizes and a chunk that is a multiple of 16 bytes")
         self.num_blocks = int(num_blocks)
@@ -88,19 +88,44 @@ class HostPool:
         self.block_stride = self.num_layers * self.chunk_bytes
         self.nbytes = self.num_blocks * self.block_stride
         hp, dp = ctypes.c_void_p(), ctypes.c_void_p()
-        _lib.check(_lib.lib().lms_host_alloc(self.nbytes, ctypes.byref(hp), ctypes.byref(dp)))
+        if _buffer is None:
+            _lib.check(_lib.lib().lms_host_alloc(self.nbytes, ctypes.byref(hp), ctypes.byref(dp)))
+            self._registered = None
+            buf = (ctypes.c_uint8 * self.nbytes).from_address(hp.value)
+            flat = np.frombuffer(buf, dtype=np.uint8)
+        else:
+            flat = _buffer
+            hp = ctypes.c_void_p(flat.ctypes.data)
+            _lib.check(_lib.lib().lms_host_register(hp, self.nbytes, ctypes.byref(dp)))
+            self._registered = flat  # keeps the caller's memory alive while it is pinned
         self.host_ptr = hp.value
         self.device_ptr = dp.value
-        buf = (ctypes.c_uint8 * self.nbytes).from_address(self.host_ptr)
-        self.array = np.frombuffer(buf, dtype=np.uint8).reshape(
-            self.num_blocks, self.num_layers, self.chunk_bytes)
+        self.array = flat.reshape(self.num_blocks, self.num_layers, self.chunk_bytes)
         self.tensor = torch.from_numpy(self.array)
+
+    @classmethod
+    def from_buffer(cls, array: np.ndarray, num_layers: int, chunk_bytes: int) -> "HostPool":
+        """Pins and maps an existing host buffer in place (``lms_host_register``) instead of
+        allocating one — for a pool that already exists, e.g. shared memory or the ``.npy``
+        memmap of the reference's disk tier staging.  ``array``: C-contiguous, 16-byte aligned,
+        a whole number of ``num_layers * chunk_bytes`` blocks; viewed as bytes."""
+        flat = np.ascontiguousarray(array).reshape(-1).view(np.uint8)
+        if flat.ctypes.data != np.asarray(array).ctypes.data:
+            raise ValueError("the buffer must be C-contiguous (it is pinned in place, not copied)")
+        per_block = int(num_layers) * int(chunk_bytes)
+        if flat.nbytes == 0 or flat.nbytes % per_block or flat.ctypes.data % 16:
+            raise ValueError("buffer size must be a whole number of blocks and 16-byte aligned")
+        return cls(flat.nbytes // per_block, num_layers, chunk_bytes, _buffer=flat)
 
     def close(self) -> None:
         if getattr(self, "host_ptr", None):
             self.tensor = None
             self.array = None
-            _lib.check(_lib.lib().lms_host_free(self.host_ptr))
+            if self._registered is None:
+                _lib.check(_lib.lib().lms_host_free(self.host_ptr))
+            else:
+                _lib.check(_lib.lib().lms_host_unregister(self.host_ptr))
+                self._registered = None
             self.host_ptr = None
             self.device_ptr = None
 

@@ -6,7 +6,7 @@ exactly.  Every function mutates its destination in place, like the reference.
 """
 from __future__ import annotations
 
-from typing import Dict, Iterable, List, Sequence, Tuple, Union
+from typing import List, Tuple
 
 import numpy as np
 

@@ -84,6 +84,32 @@ def test_swap_layer_range_and_empty():
         pool.close()
 
 
+def test_host_pool_from_existing_buffer():
+    """A pool pinned in place over caller-owned memory (lms_host_register) behaves like an
+    allocated one, and the caller sees the swapped-out bytes in its own array."""
+    shape = W.SHAPES["llama31_8b_swap"].scaled(num_layers=2, num_blocks=16, num_kv_heads=1)
+    words, gpu = make_gpu_cache(shape, 67)
+    backing = np.zeros((6 * 2 * shape.chunk_bytes + 4096,), dtype=np.uint8)
+    off = (-backing.ctypes.data) % 4096                      # page-align the pool inside it
+    mine = backing[off:off + 6 * 2 * shape.chunk_bytes]
+    pool = HostPool.from_buffer(mine, 2, shape.chunk_bytes)
+    try:
+        assert pool.num_blocks == 6 and pool.host_ptr == mine.ctypes.data
+        pairs = np.array([[9, 4], [0, 1]], dtype=np.int64)
+        cache_ops.swap_blocks(gpu, pool, pairs, "out")
+        torch.cuda.synchronize()
+        want = np.zeros((6, 2, shape.chunk_bytes // 2), np.uint16)
+        cache_oracle.swap_out(words.reshape(2, 16, -1), want, pairs)
+        assert np.array_equal(mine.view(np.uint16).reshape(want.shape), want)
+        cache_ops.swap_blocks(gpu, pool, np.array([[4, 15]], dtype=np.int64), "in")
+        torch.cuda.synchronize()
+        assert np.array_equal(to_words(gpu).reshape(2, 16, -1)[:, 15], words.reshape(2, 16, -1)[:, 9])
+    finally:
+        pool.close()
+    with pytest.raises(ValueError):
+        HostPool.from_buffer(np.zeros(100, np.uint8), 2, shape.chunk_bytes)
+
+
 def test_kvworker_copy_kv_with_layer_events():
     """Write-through then fetch, one launch per layer, ordered by per-layer events the way the
     model's forward hooks and the KV worker hand layers to each other."""
