@@ -448,11 +448,11 @@ def host_pool_blocks(chunk_layers_bytes: int, want_blocks: int, cap_gib: float) 
                 avail = min(avail, int(v)) if avail else int(v)
         except Exception:
             pass
-    budget = int(cap_gib * (1 << 30))
+    limit = int(cap_gib * (1 << 30))
     if avail:
-        budget = min(budget, int(avail * 0.35))
+        limit = min(limit, int(avail * 0.35))
     n = want_blocks
-    while n > 1 and n * chunk_layers_bytes > budget:
+    while n > 1 and n * chunk_layers_bytes > limit:
         n //= 2
     return n
 

@@ -1,7 +1,7 @@
 """Runs LMServe's own Triton cache kernels on CPU through the Triton interpreter.
 
-Only usable where the LMServe source tree is present (``LMSERVE_SRC``, default
-``/root/reference``); it is what ``tests/golden/make_golden.py`` uses to produce the
+Only usable where the LMServe source tree is present (the directory named by ``LMSERVE_SRC``,
+or a ``reference`` directory next to this repository); it is what ``tests/golden/make_golden.py`` uses to produce the
 committed golden vectors, and what the optional cross-check test uses when the tree is
 there.  ``cache_kernels.py`` is loaded by file path because importing the ``llm_worker``
 package pulls in pycuda and nixl; the launch arguments are those of the reference
@@ -18,7 +18,10 @@ KERNEL_FILE = "runtime/worker/llm_worker/ops/triton/cache_kernels.py"
 
 
 def reference_root() -> Path:
-    return Path(os.environ.get("LMSERVE_SRC", "/root/reference"))
+    env = os.environ.get("LMSERVE_SRC")
+    if env:
+        return Path(env)
+    return Path(__file__).resolve().parents[2] / "reference"
 
 
 def available() -> bool:

@@ -1,7 +1,7 @@
 """Generates the golden vectors in this directory from LMServe's own Triton kernels.
 
-Run in a container that has the LMServe source tree (``LMSERVE_SRC``, default
-``/root/reference``) and triton:
+Run where the LMServe source tree is available (``LMSERVE_SRC``, or a ``reference`` directory
+next to this repository) and triton is installed:
 
     TRITON_INTERPRET=1 python tests/golden/make_golden.py
 
