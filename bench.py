@@ -347,6 +347,7 @@ def run_ours(args):
         cpu = None
         if world == 1 and not args.no_cpu_baseline:
             cpu = cpu_baseline(bounded_seconds=10.0)
+            cpu["other_ops"] = cpu_other_ops(cpu["cores"])
         achieved = step_bytes / (ms_per_step * 1e-3) / 1e9
         line = {
             "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world,
@@ -728,6 +729,44 @@ def cpu_baseline(bounded_seconds: float):
             "sample": f"{len(times)} full decode steps (32 layers x 256 tokens, 64 MiB each) as torch "
                       f"index_copy_ on bf16 CPU tensors; cache pool reduced to the {s.num_blocks} touched blocks",
             "ms_per_step": round(med * 1e3, 4)}
+
+
+def cpu_other_ops(threads: int, seconds_each: float = 4.0):
+    """Bounded samples of the other cache ops as torch index ops on the host cores: copy-on-write
+    (index_select + index_copy_ on the block axis) and the swap as a host-to-host gather between
+    a layer-major and a block-major tensor (the PCIe hop has no CPU analogue)."""
+    from oracle import torch_ref
+    torch.set_num_threads(threads)
+    out = {}
+    w = W.config3()
+    s = w.shape.scaled(num_layers=2)          # 2 of 28 layers, all 4096 pairs: 256 MiB written
+    blocks, inv = np.unique(w.pairs.reshape(-1), return_inverse=True)
+    pairs = torch.from_numpy(inv.reshape(-1, 2).astype(np.int64))
+    kv = torch.zeros(s.num_layers, len(blocks), s.chunk_bytes // 2, dtype=torch.bfloat16)
+    nbytes = (len(pairs) + len(np.unique(w.pairs[:, 0]))) * s.num_layers * s.chunk_bytes
+
+    def timed_cpu(fn):
+        fn()
+        ts, end = [], time.perf_counter() + seconds_each
+        while time.perf_counter() < end and len(ts) < 200:
+            t0 = time.perf_counter()
+            fn()
+            ts.append(time.perf_counter() - t0)
+        return statistics.median(ts), len(ts)
+
+    med, n = timed_cpu(lambda: torch_ref.copy_blocks(kv, pairs))
+    out["copy_blocks_cow"] = {"GB/s": round(nbytes / med / 1e9, 3), "ms": round(med * 1e3, 3),
+                              "sample": f"{n} runs of 4096 pairs x 2 layers x 32 KiB (2 of the 28 layers)"}
+    del kv
+    s4 = W.SHAPES["llama31_8b_swap"].scaled(num_layers=4, num_blocks=2048)
+    sw = W.make_swap(s4, 2048, 1024, seed=1004)   # 1024 blocks x 4 layers x 64 KiB = 256 MiB
+    gpu = torch.zeros(s4.num_layers, s4.num_blocks, s4.chunk_bytes // 2, dtype=torch.bfloat16)
+    host = torch.zeros(2048, s4.num_layers, s4.chunk_bytes // 2, dtype=torch.bfloat16)
+    nb = len(sw.out_pairs) * s4.num_layers * s4.chunk_bytes
+    med, n = timed_cpu(lambda: torch_ref.swap_out(gpu, host, sw.out_pairs))
+    out["swap_out_host_gather"] = {"GB/s": round(nb / med / 1e9, 3), "ms": round(med * 1e3, 3),
+                                   "sample": f"{n} runs of 1024 blocks x 4 layers x 64 KiB, host to host"}
+    return out
 
 
 def run_reference(args):

@@ -496,3 +496,30 @@ def test_peer_enable_errors_are_statuses():
     assert rc in (_lib.LMS_ERR_CUDA, _lib.LMS_ERR_PEER)
     x = torch.ones(8, device=DEV)                                # context still fine
     assert float(x.sum()) == 8.0
+
+
+def test_other_element_sizes_float32_and_int8():
+    """The kernels move bytes: a float32 cache (the reference's dtype map also lists it,
+    kv_worker.py:17-22) and a 1-byte cache go through the same path."""
+    g = torch.Generator(device="cpu").manual_seed(3)
+    for dtype, D in ((torch.float32, 32), (torch.int8, 64), (torch.float64, 16)):
+        L_, NB, BS, H, T = 2, 12, 4, 2, 17
+        make = (lambda *s: torch.randn(*s, generator=g).to(dtype)) if dtype.is_floating_point else \
+            (lambda *s: torch.randint(-100, 100, s, generator=g).to(dtype))
+        cache, key, value = make(L_, NB, 2, BS, H, D), make(L_, T, H, D), make(L_, T, H, D)
+        slots = torch.randperm(NB * BS, generator=g)[:T]
+        slots[4] = -1
+        want = cache.clone()
+        for l in range(L_):
+            for t in range(T):
+                s = int(slots[t])
+                if s >= 0:
+                    want[l, s // BS, 0, s % BS] = key[l, t]
+                    want[l, s // BS, 1, s % BS] = value[l, t]
+        got = cache.to(DEV)
+        cache_ops.reshape_and_cache_layers(key.to(DEV), value.to(DEV), got, slots.to(DEV))
+        cache_ops.copy_blocks(got, {3: [10, 11]})
+        want[:, 10] = want[:, 3]
+        want[:, 11] = want[:, 3]
+        torch.cuda.synchronize()
+        assert torch.equal(got.cpu().view(torch.uint8), want.view(torch.uint8)), dtype
