@@ -28,8 +28,8 @@ namespace lms {
 namespace {
 
 template <class T2>
-struct Pack8 {
-  T2 v[4];  // 8 elements = 16 bytes
+struct __align__(16) Pack8 {
+  T2 v[4];  // 8 elements = 16 bytes, moved as one 16-byte access
 };
 
 __device__ __forceinline__ void ld16(void* dst, const char* p) {
