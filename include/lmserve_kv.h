@@ -70,7 +70,11 @@ typedef enum lms_status {
 #define LMS_TUNE_XFER_VARIANT 8  /* as LMS_TUNE_COPY_VARIANT */
 #define LMS_TUNE_WRITE_VPT 9     /* vectors per thread per pipeline batch of the cache write: 2, 4, 8 */
 #define LMS_TUNE_SWAP_VARIANT 10 /* as LMS_TUNE_COPY_VARIANT, both directions */
-#define LMS_TUNE__COUNT 11
+#define LMS_TUNE_WRITE_PDL 11    /* 1 (built-in) = launch the untiled cache write and the rotary kernel
+                                    with programmatic stream serialization: the grid becomes resident
+                                    while the previous kernel drains and still waits for that kernel
+                                    before touching memory, so stream order is unchanged; 2 = off */
+#define LMS_TUNE__COUNT 12
 
 /* Library version (LMS_VERSION of the build). */
 int lms_version(void);

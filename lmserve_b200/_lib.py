@@ -35,6 +35,7 @@ TUNE_XFER_CTAS_PER_SM = 7
 TUNE_XFER_VARIANT = 8
 TUNE_WRITE_VPT = 9
 TUNE_SWAP_VARIANT = 10
+TUNE_WRITE_PDL = 11
 
 # name -> (restype, argtypes); one entry per declaration in include/lmserve_kv.h
 SIGNATURES = {

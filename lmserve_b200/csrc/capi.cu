@@ -177,7 +177,8 @@ int write_launch(WriteParams p, void* stream) {
   const int variant = tuned_variant(LMS_TUNE_WRITE_VARIANT, -1);  // -1: launch_write chooses
   const int tile = tuned(LMS_TUNE_WRITE_TILE_BYTES, 0);
   const int vpt = tuned(LMS_TUNE_WRITE_VPT, 2);
-  LMS_CUDA(launch_write(p, variant, tile, vpt, ds->sms, (cudaStream_t)stream));
+  const bool pdl = tuned(LMS_TUNE_WRITE_PDL, 1) == 1;
+  LMS_CUDA(launch_write(p, variant, tile, vpt, ds->sms, pdl, (cudaStream_t)stream));
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return LMS_OK;
 }
@@ -570,7 +571,7 @@ int lms_rope_and_cache(const void* query, const void* key, const void* value,
   p.is_bf16 = dtype;
   p.err = ds->err.load(std::memory_order_relaxed);
   p.checks = g_checks.load(std::memory_order_relaxed);
-  LMS_CUDA(launch_rope_cache(p, (cudaStream_t)stream));
+  LMS_CUDA(launch_rope_cache(p, tuned(LMS_TUNE_WRITE_PDL, 1) == 1, (cudaStream_t)stream));
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return LMS_OK;
 }

@@ -55,9 +55,10 @@ struct WriteParams {
 };
 
 // variant: 0 = 16-byte vectors, 1 = 32-byte vectors, 2 = bulk copies;
-// vpt: vectors per thread per pipeline batch (2, 4 or 8)
+// vpt: vectors per thread per pipeline batch (2, 4 or 8);
+// pdl: launch the untiled kernel with programmatic stream serialization
 cudaError_t launch_write(const WriteParams& p, int variant, int tile_bytes,
-                         int vpt, int sms, cudaStream_t stream);
+                         int vpt, int sms, bool pdl, cudaStream_t stream);
 
 // ------------------------------------------------------------ chunk copies
 // One kernel family serves copy_blocks, swap-out, swap-in and transfer: every
@@ -112,7 +113,7 @@ struct RopeParams {
   int checks;
 };
 
-cudaError_t launch_rope_cache(const RopeParams& p, cudaStream_t stream);
+cudaError_t launch_rope_cache(const RopeParams& p, bool pdl, cudaStream_t stream);
 
 // One warp waits (bounded) on an mbarrier that is never completed; see lms_selftest_bounded_wait.
 cudaError_t launch_wait_selftest(ErrRecord* err, unsigned long long limit_ns, cudaStream_t stream);

@@ -50,6 +50,10 @@ template <class T2, int THREADS>
 __global__ void __launch_bounds__(THREADS)
 rope_cache_kernel(const RopeParams p, const int items_per_head, const int heads_total,
                   const long long n_items) {
+  // Programmatic dependent launch, as in the cache-write kernel: resident early, but nothing
+  // is touched before the previous kernel of the stream has completed.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const long long item = (long long)blockIdx.x * THREADS + threadIdx.x;
   if (item >= n_items) return;
   // item = (t * heads_total + h) * items_per_head + j
@@ -142,7 +146,7 @@ rope_cache_kernel(const RopeParams p, const int items_per_head, const int heads_
 
 }  // namespace
 
-cudaError_t launch_rope_cache(const RopeParams& p_in, cudaStream_t stream) {
+cudaError_t launch_rope_cache(const RopeParams& p_in, bool pdl, cudaStream_t stream) {
   RopeParams p = p_in;
   p.block_shift = -1;
   if (p.block_size > 0 && (p.block_size & (p.block_size - 1)) == 0) {
@@ -157,13 +161,22 @@ cudaError_t launch_rope_cache(const RopeParams& p_in, cudaStream_t stream) {
   if (n_items <= 0) return cudaSuccess;
   const long long ctas = (n_items + THREADS - 1) / THREADS;
   if (ctas > 0x7fffffffll) return cudaErrorInvalidConfiguration;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)ctas);
+  cfg.blockDim = dim3(THREADS);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  if (pdl) {
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
   if (p.is_bf16)
-    rope_cache_kernel<__nv_bfloat162, THREADS>
-        <<<(unsigned)ctas, THREADS, 0, stream>>>(p, items_per_head, heads_total, n_items);
-  else
-    rope_cache_kernel<__half2, THREADS>
-        <<<(unsigned)ctas, THREADS, 0, stream>>>(p, items_per_head, heads_total, n_items);
-  return cudaGetLastError();
+    return cudaLaunchKernelEx(&cfg, rope_cache_kernel<__nv_bfloat162, THREADS>, p,
+                              items_per_head, heads_total, n_items);
+  return cudaLaunchKernelEx(&cfg, rope_cache_kernel<__half2, THREADS>, p, items_per_head,
+                            heads_total, n_items);
 }
 
 }  // namespace lms

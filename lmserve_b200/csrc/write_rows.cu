@@ -181,6 +181,13 @@ template <class Vec, int THREADS, bool POW2>
 __global__ void __launch_bounds__(THREADS)
 write_rows_direct(const WriteParams p, const int row_vecs, const int row_shift,
                   const long long n_vec_total) {
+  // Programmatic dependent launch (a no-op when the launch does not ask for it): this grid
+  // may have been made resident while the previous kernel of the stream was still running.
+  // Nothing is read or written before that kernel has completed and its writes are visible,
+  // so stream order is exactly what it would be without the attribute; only the launch
+  // latency is hidden.  The kernel that follows this one is allowed to do the same.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const long long v = (long long)blockIdx.x * THREADS + threadIdx.x;
   if (v >= n_vec_total) return;
   // v = ((layer * T + t) * 2 + kv) * row_vecs + c
@@ -325,20 +332,29 @@ cudaError_t launch_vec(WriteParams p, int tile_bytes, int sms, cudaStream_t stre
 }
 
 template <class Vec>
-cudaError_t launch_direct(const WriteParams& p, cudaStream_t stream) {
+cudaError_t launch_direct(const WriteParams& p, bool pdl, cudaStream_t stream) {
   constexpr int THREADS = 256;
   const int row_vecs = p.row_bytes / Vec::kBytes;
   const int row_shift = ilog2_exact(row_vecs);
   const long long n_vec = (long long)p.num_layers * p.num_tokens * 2 * row_vecs;
   const long long ctas = (n_vec + THREADS - 1) / THREADS;
   if (ctas > 0x7fffffffll) return cudaErrorInvalidConfiguration;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)ctas);
+  cfg.blockDim = dim3(THREADS);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  if (pdl) {
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
   if (row_shift >= 0)
-    write_rows_direct<Vec, THREADS, true>
-        <<<(unsigned)ctas, THREADS, 0, stream>>>(p, row_vecs, row_shift, n_vec);
-  else
-    write_rows_direct<Vec, THREADS, false>
-        <<<(unsigned)ctas, THREADS, 0, stream>>>(p, row_vecs, row_shift, n_vec);
-  return cudaGetLastError();
+    return cudaLaunchKernelEx(&cfg, write_rows_direct<Vec, THREADS, true>, p, row_vecs,
+                              row_shift, n_vec);
+  return cudaLaunchKernelEx(&cfg, write_rows_direct<Vec, THREADS, false>, p, row_vecs,
+                            row_shift, n_vec);
 }
 
 template <class Vec>
@@ -352,7 +368,7 @@ cudaError_t launch_vec_vpt(const WriteParams& p, int tile_bytes, int vpt, int sm
 }  // namespace
 
 cudaError_t launch_write(const WriteParams& p_in, int variant, int tile_bytes,
-                         int vpt, int sms, cudaStream_t stream) {
+                         int vpt, int sms, bool pdl, cudaStream_t stream) {
   WriteParams p = p_in;
   p.block_shift = ilog2_exact(p.block_size);
 
@@ -375,8 +391,9 @@ cudaError_t launch_write(const WriteParams& p_in, int variant, int tile_bytes,
     variant = a32 ? 3 : (total <= (16ll << 20) ? 4 : 0);
   }
   if (variant == 1 && !a32) variant = 0;
-  if (variant == 3) return a32 ? launch_direct<V32>(p, stream) : launch_direct<V16>(p, stream);
-  if (variant == 4) return launch_direct<V16>(p, stream);
+  if (variant == 3)
+    return a32 ? launch_direct<V32>(p, pdl, stream) : launch_direct<V16>(p, pdl, stream);
+  if (variant == 4) return launch_direct<V16>(p, pdl, stream);
 
   if (variant == 2) {
     // piece = the largest power-of-two divisor of the row, capped at 1 KiB

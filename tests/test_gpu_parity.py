@@ -25,7 +25,7 @@ VARIANTS = [0, 1, 2, 3, 4]  # tiled 16/32-byte vectors, bulk (TMA) copies, until
 def _reset_tuning():
     yield
     L = _lib.lib()
-    for key in range(1, 11):
+    for key in range(1, 12):
         L.lms_set_tuning(key, -1)
     L.lms_set_debug_checks(0)
 
@@ -523,3 +523,28 @@ def test_other_element_sizes_float32_and_int8():
         want[:, 11] = want[:, 3]
         torch.cuda.synchronize()
         assert torch.equal(got.cpu().view(torch.uint8), want.view(torch.uint8)), dtype
+
+
+@pytest.mark.parametrize("pdl", [1, 2])
+def test_back_to_back_writes_to_the_same_slots_land_in_stream_order(pdl):
+    """With programmatic dependent launch (1) the next kernel's grid is resident before the
+    previous one has finished; it must still not overtake it.  Eight writes of different data
+    to the same slots, repeated: the last one wins, every time."""
+    _lib.lib().lms_set_tuning(_lib.TUNE_WRITE_PDL, pdl)
+    shape = W.SHAPES["llama31_8b"].scaled(num_layers=8, num_blocks=4096)
+    w = W.make_decode_write(shape, 128, 16, 400, seed=95)
+    slots = torch.from_numpy(w.slot_mapping).to(DEV)
+    kv = torch.zeros(shape.cache_shape, dtype=torch.bfloat16, device=DEV)
+    keys = [torch.randn(8, 128, 8, 128, device=DEV).to(torch.bfloat16) for _ in range(8)]
+    vals = [torch.randn(8, 128, 8, 128, device=DEV).to(torch.bfloat16) for _ in range(8)]
+    plans = [cache_ops.WritePlan(keys[j], vals[j], kv, slots) for j in range(8)]
+    sp = torch.cuda.current_stream().cuda_stream
+    blk, ent = slots // 16, slots % 16
+    for trial in range(10):
+        order = np.random.default_rng(trial).permutation(8)
+        for j in order:
+            plans[j].run(sp)
+        last = int(order[-1])
+        torch.cuda.synchronize()
+        assert torch.equal(kv[:, blk, 0, ent].view(torch.int16), keys[last].view(torch.int16)), trial
+        assert torch.equal(kv[:, blk, 1, ent].view(torch.int16), vals[last].view(torch.int16)), trial
