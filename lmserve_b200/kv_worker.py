@@ -185,6 +185,36 @@ def _lib_handle_bytes() -> int:
     return 64
 
 
+@dataclass
+class KVWorkerParams:
+    """What the model process hands to the KV process so that it can map the model's cache and
+    its per-layer events: the GPU-facing fields of ``KVWorkerParams`` (``kv_worker.py:34-45``).
+    ``kv_cache_metadata`` is the tuple ``UntypedStorage._share_cuda_()`` returns
+    (``model_worker.py:284``); the event handles come from ``Event.ipc_handle()`` of events
+    created with ``interprocess=True`` (``model_worker.py:232-251,285-290``).  The queues of the
+    reference carry only wake-up tokens for its polling loops; here ordering is by the events
+    themselves, so no queue is needed."""
+    kv_cache_metadata: tuple
+    cache_shape: tuple            # (num_layers, num_gpu_blocks, 2, block_size, H, D)
+    dtype: torch.dtype
+    num_host_blocks: int = 0
+    device_index: int = 0
+    pre_event_handles: Sequence[bytes] = ()
+    post_event_handles: Sequence[bytes] = ()
+
+    @classmethod
+    def from_cache(cls, kv_caches: torch.Tensor, num_host_blocks: int = 0,
+                   pre_events: Sequence[torch.cuda.Event] = (),
+                   post_events: Sequence[torch.cuda.Event] = ()) -> "KVWorkerParams":
+        """Called in the model process (``ModelWorker.init_cache``, ``model_worker.py:278-306``)."""
+        cache_ops._require_cuda("kv_caches", kv_caches)
+        if not kv_caches.is_contiguous() or kv_caches.storage_offset() != 0:
+            raise ValueError("the shared cache must be a whole contiguous allocation")
+        return cls(kv_caches.untyped_storage()._share_cuda_(), tuple(kv_caches.shape), kv_caches.dtype,
+                   num_host_blocks, kv_caches.device.index,
+                   [e.ipc_handle() for e in pre_events], [e.ipc_handle() for e in post_events])
+
+
 class KVWorker:
     """Per-GPU mover of KV blocks, API-compatible with the GPU-facing part of LMServe's
     ``KVWorker`` (``kv_worker.py:88-195,249-295,336-415``).
@@ -212,6 +242,22 @@ class KVWorker:
             (Device.GPU, Device.Host): self.save_kv_blocks_to_host,
             (Device.Host, Device.GPU): self.load_kv_blocks_from_host,
         }
+
+    @classmethod
+    def from_params(cls, name: str, params: KVWorkerParams) -> "KVWorker":
+        """Built in the KV process: maps the model process's cache through CUDA IPC
+        (``kv_worker.py:104-108``) and opens its interprocess events (``kv_worker.py:140-147``).
+        The events are available as ``worker.pre_events`` / ``worker.post_events``."""
+        dev = torch.device("cuda", params.device_index)
+        with torch.cuda.device(dev):
+            storage = torch.UntypedStorage._new_shared_cuda(*params.kv_cache_metadata)
+            cache = torch.empty(0, dtype=params.dtype, device=dev)
+            cache.set_(storage)
+            cache = cache.view(*params.cache_shape)
+            worker = cls(name, cache, params.num_host_blocks)
+            worker.pre_events = [torch.cuda.Event.from_ipc_handle(dev, h) for h in params.pre_event_handles]
+            worker.post_events = [torch.cuda.Event.from_ipc_handle(dev, h) for h in params.post_event_handles]
+        return worker
 
     # -- swap -----------------------------------------------------------------
     def load_kv_blocks_from_host(self, block_mappings, stream: Optional[torch.cuda.Stream] = None,

@@ -171,6 +171,58 @@ def test_transfer_blocks_across_devices():
     assert np.array_equal(to_words(dst), want)
 
 
+def _kv_process(params, out_pairs, in_pairs, q):
+    """Child = the KV process: maps the parent's cache and events, writes blocks through to its
+    host pool as the parent's post-events fire, then fetches them back into other blocks and
+    records the pre-events."""
+    try:
+        import torch
+        from lmserve_b200.kv_worker import Device, KVWorker
+        w = KVWorker.from_params("kv0", params)
+        w.copy_kv([out_pairs], Device.GPU, Device.Host, post_events=w.post_events)
+        w.dtoh_stream.synchronize()
+        w.copy_kv([in_pairs], Device.Host, Device.GPU, pre_events=w.pre_events)
+        w.htod_stream.synchronize()
+        host_sum = int(w.host_pool.array[out_pairs[:, 1]].astype("int64").sum())
+        w.close()
+        q.put(("ok", host_sum))
+    except Exception as e:  # pragma: no cover - reported to the parent
+        q.put(("error", repr(e)))
+
+
+def test_kv_process_maps_the_model_process_cache_and_events():
+    """The reference's two-process layout: the model process owns the cache and the per-layer
+    events, the KV process maps both (CUDA IPC) and swaps blocks, ordered by the events."""
+    from lmserve_b200.kv_worker import KVWorkerParams
+    shape = W.SHAPES["llama31_8b_swap"].scaled(num_layers=3, num_blocks=32, num_kv_heads=2)
+    words, gpu = make_gpu_cache(shape, 83)
+    L_ = shape.num_layers
+    pre = [torch.cuda.Event(interprocess=True) for _ in range(L_)]
+    post = [torch.cuda.Event(interprocess=True) for _ in range(L_)]
+    for e in post:                       # "attention of layer l is done"
+        e.record(torch.cuda.current_stream())
+    torch.cuda.synchronize()
+    params = KVWorkerParams.from_cache(gpu, num_host_blocks=8, pre_events=pre, post_events=post)
+    out_pairs = np.array([[3, 0], [17, 5], [30, 7]], dtype=np.int64)
+    in_pairs = np.array([[5, 1], [0, 2], [7, 31]], dtype=np.int64)
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    p = ctx.Process(target=_kv_process, args=(params, out_pairs, in_pairs, q))
+    p.start()
+    status, payload = q.get(timeout=300)
+    p.join(timeout=60)
+    assert status == "ok", payload
+    for e in pre:                        # the model would wait on these before layer l
+        torch.cuda.current_stream().wait_event(e)
+    torch.cuda.synchronize()
+    gw = words.reshape(L_, 32, -1).copy()
+    hw = np.zeros((8, L_, shape.chunk_bytes // 2), np.uint16)
+    cache_oracle.swap_out(gw, hw, out_pairs)
+    assert payload == int(hw[out_pairs[:, 1]].view(np.uint8).astype(np.int64).sum())
+    cache_oracle.swap_in(gw, hw, in_pairs)
+    assert np.array_equal(to_words(gpu).reshape(gw.shape), gw)
+
+
 def _pusher(desc_bytes, seed, pairs_src, q):
     """Child process = the prefill-side worker: builds its own cache and pushes blocks into the
     parent's cache through the IPC descriptor."""
