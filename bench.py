@@ -337,6 +337,8 @@ def run_ours(args):
             if torch.cuda.device_count() >= 2 and "transfer_local" in ops_wanted:
                 extra(["transfer_local"], lambda: bench_transfer_local(comm, stream, cache_view, dev,
                                                                        args, sampler))
+            if "flashinfer" in ops_wanted:
+                extra(["flashinfer"], lambda: bench_vs_flashinfer(comm, stream, cache_view, dev, args, sampler))
         extra(["tp8"], lambda: bench_tp8_decode(comm, stream, cache_view, dev, rank, world, peak_gbs,
                                                 args, sampler))
         if world >= 2 and world % 2 == 0:
@@ -595,6 +597,72 @@ def bench_rope_fusion(comm, stream, cache_view, dev, args, sampler):
     return out
 
 
+def bench_vs_flashinfer(comm, stream, cache_view, dev, args, sampler):
+    """The decode step's 32 per-layer cache writes through flashinfer.append_paged_kv_cache (the
+    call LMServe makes, models/layers/attention.py:76-85) and through this library, eager and
+    replayed from CUDA graphs, on the same rotating inputs.  Not part of --ops all: flashinfer
+    compiles its kernel on first use."""
+    import flashinfer
+    from lmserve_b200.ops import cache_ops
+    s = W.SHAPES["llama31_8b"]
+    kv = cache_view(s)
+    Lyr, T = s.num_layers, 256
+    sets = []
+    for i in range(ROTATE):
+        w = W.config2(seed=4002 + 17 * i)
+        indptr, indices = W.paged_metadata(w.tables.tables)
+        sets.append(dict(
+            key=torch.randn(Lyr, T, s.num_kv_heads, s.head_dim, device=dev, dtype=torch.bfloat16),
+            value=torch.randn(Lyr, T, s.num_kv_heads, s.head_dim, device=dev, dtype=torch.bfloat16),
+            slots=torch.from_numpy(w.slot_mapping).to(dev),
+            batch=torch.arange(T, dtype=torch.int32, device=dev),
+            pos=torch.from_numpy(w.context_lens.astype(np.int32)).to(dev),
+            indptr=torch.from_numpy(indptr).to(dev), indices=torch.from_numpy(indices).to(dev),
+            last=torch.from_numpy(((w.context_lens % 16) + 1).astype(np.int32)).to(dev)))
+    plans = [[cache_ops.WritePlan(d["key"][l], d["value"][l], kv[l], d["slots"]) for l in range(Lyr)]
+             for d in sets]
+
+    def fi(j):
+        d = sets[j]
+        for l in range(Lyr):
+            flashinfer.append_paged_kv_cache(d["key"][l], d["value"][l], d["batch"], d["pos"], kv[l],
+                                             d["indices"], d["indptr"], d["last"])
+
+    def ours_paged(j):
+        d = sets[j]
+        for l in range(Lyr):
+            cache_ops.append_paged_kv_cache(d["key"][l], d["value"][l], d["batch"], d["pos"], kv[l],
+                                            d["indices"], d["indptr"], d["last"])
+
+    def ours_plan(j):
+        sp = torch.cuda.current_stream().cuda_stream
+        for p in plans[j]:
+            p.run(sp)
+
+    fi(0)
+    torch.cuda.synchronize()
+    d0 = sets[0]
+    blk, ent = d0["slots"] // 16, d0["slots"] % 16
+    same = bool(torch.equal(kv[:, blk, 0, ent].view(torch.int16), d0["key"].view(torch.int16)))
+    out = {"flashinfer_version": getattr(flashinfer, "__version__", "?"), "flashinfer_result_matches": same}
+    for name, fn in (("flashinfer", fi), ("ours_flashinfer_signature", ours_paged), ("ours_write_plan", ours_plan)):
+        fn(0)
+        ms_e = timed(comm, stream, lambda i: fn(i % ROTATE), 30, 3, sampler) / 30
+        graphs = []
+        side = torch.cuda.Stream()
+        side.wait_stream(stream)
+        for j in range(ROTATE):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                fn(j)
+            graphs.append(g)
+        stream.wait_stream(side)
+        torch.cuda.synchronize()
+        ms_g = timed(comm, stream, lambda i: graphs[i % ROTATE].replay(), 100, 3, sampler) / 100
+        out[name] = {"eager_us_per_layer": ms_e * 1e3 / Lyr, "graph_us_per_layer": ms_g * 1e3 / Lyr}
+    return {"vs_flashinfer_per_layer_decode_write": out}
+
+
 def bench_tp8_decode(comm, stream, cache_view, dev, rank, world, peak_gbs, args, sampler):
     """Llama-3.1-70B under TP=8: one KV head per GPU (256-byte rows), 80 layers, batch 512."""
     from lmserve_b200.ops import cache_ops
@@ -807,7 +875,8 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--ops", default="all",
                     help="comma list of extra workloads: all, none, prefill_cow, swap, rope, tp8, "
-                         "transfer (multi-rank), transfer_local (two GPUs in one process; not in 'all')")
+                         "transfer (multi-rank), transfer_local (two GPUs in one process; not in 'all'), "
+                         "flashinfer (comparison with flashinfer.append_paged_kv_cache; not in 'all')")
     ap.add_argument("--host-pool-gib", type=float, default=32.0,
                     help="cap of the pinned host pool of the swap workload")
     ap.add_argument("--no-cpu-baseline", action="store_true")
