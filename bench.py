@@ -250,6 +250,15 @@ def run_ours(args):
         ops["decode_write_eager_stream"] = {"us_per_step": ms_s * 1e3,
                                             "GB/s": step_bytes / (ms_s * 1e-3) / 1e9}
 
+        # yardstick: a plain contiguous device copy of the same volume (32 MiB in, 32 MiB out),
+        # same rotation of sources, torch's copy kernel
+        flat_src = [torch.cat((keys[j].view(-1), vals[j].view(-1))) for j in range(2)]
+        flat_dst = [torch.empty_like(t) for t in flat_src]
+        ms_c = timed(comm, stream, lambda i: flat_dst[i % 2].copy_(flat_src[i % 2]), args.steps, 3, sampler) / args.steps
+        ops["contiguous_copy_same_volume_torch"] = {"us_per_copy": ms_c * 1e3,
+                                                    "GB/s": step_bytes / (ms_c * 1e-3) / 1e9}
+        del flat_src, flat_dst
+
         # the same step through the general-purpose wrapper (argument checks on every call)
         ms_w = timed(comm, stream, lambda i: cache_ops.reshape_and_cache_layers(
             keys[i % ROTATE], vals[i % ROTATE], kv, slots[i % ROTATE]), args.steps, 3, sampler) / args.steps
