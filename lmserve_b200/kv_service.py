@@ -13,9 +13,9 @@ Mirrors ``KVWorkerService`` of ``runtime/worker/llm_worker/cli.py:145-229``:
 synchronised; ``GetDescriptors`` returns the serialized GPU-direct descriptor; ``PushKV`` returns
 the boolean of ``KVWorker.push_kv``.  ``GetLocalAgentMetadata`` / ``AddRemoteAgentMetadata``
 exist for the NIXL handshake of the reference; with CUDA-IPC descriptors there is no agent to
-register, so they echo the worker's name.  ``PullKV`` is answered ``success=False``: the
-reference's own handler is unreachable (it reads a field the message does not have,
-``cli.py:219-221``) and the Rust side never calls it (``worker.rs:521``).
+register, so they echo the worker's name.  ``PullKV`` reads the message's ``descs`` field (the
+reference's handler reads a field the message does not have, ``cli.py:219-221``, and the Rust
+side never calls it, ``worker.rs:521``) and runs ``KVWorker.pull_kv``.
 """
 from __future__ import annotations
 
@@ -144,7 +144,10 @@ class KVWorkerService:
         return PushKVResponse(success=bool(ok))
 
     def PullKV(self, request, context):
-        return PullKVResponse(success=False)
+        ok = self.worker.pull_kv(request.peer_name, request.descs, list(request.block_ids))
+        if ok:
+            self.worker.push_stream.synchronize()
+        return PullKVResponse(success=bool(ok))
 
 
 def add_kv_worker_servicer(servicer, server: grpc.Server) -> None:

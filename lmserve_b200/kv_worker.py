@@ -354,6 +354,40 @@ class KVWorker:
             print(f"Posting transfer failed. {e}")
             return False
 
+    def pull_kv(self, peer_name: str, remote_descs: bytes, block_ids: Sequence[int],
+                stream: Optional[torch.cuda.Stream] = None) -> bool:
+        """The mirror image of :meth:`push_kv` (role of ``kv_worker.py:417-454``, NIXL "READ"):
+        this GPU reads the blocks the peer's descriptor lists out of the peer's cache, over
+        NVLink, into its own blocks ``block_ids``.  The kernel runs here, with plain loads from
+        the mapped peer memory."""
+        try:
+            desc = CacheDescriptor.deserialize(remote_descs)
+            try:
+                pairs = build_push_pairs(block_ids, desc.block_ids)   # (local, remote)
+            except ValueError as e:
+                print(f"Creating transfer failed. {e}")
+                return False
+            with torch.cuda.device(self.device):
+                peer = self._peers.get(peer_name)
+                if peer is None:
+                    peer = PeerCache(desc)
+                    self._peers[peer_name] = peer
+                if peer.num_layers != self.num_layers or peer.chunk_bytes != self.chunk_bytes:
+                    print("Creating transfer failed. cache geometries differ")
+                    return False
+                table = np.ascontiguousarray(pairs[:, ::-1])              # (remote src, local dst)
+                s = stream or self.push_stream
+                with torch.cuda.stream(s):
+                    _lib.check(_lib.lib().lms_transfer_blocks_host(
+                        peer.device_ptr, peer.layer_stride, peer.block_stride,
+                        self.gpu_kv_caches.data_ptr(), self.layer_stride, self.block_stride,
+                        self.chunk_bytes, self.num_layers, table.ctypes.data, len(table),
+                        peer.num_blocks, self.num_gpu_blocks, s.cuda_stream))
+            return True
+        except _lib.LmsError as e:
+            print(f"Posting transfer failed. {e}")
+            return False
+
     def close(self) -> None:
         for p in self._peers.values():
             p.close()

@@ -223,6 +223,48 @@ def test_kv_process_maps_the_model_process_cache_and_events():
     assert np.array_equal(to_words(gpu).reshape(gw.shape), gw)
 
 
+def _puller(desc_bytes, seed, local_blocks, q):
+    """Child = the decode-side worker pulling blocks out of the parent's (prefill) cache."""
+    try:
+        import numpy as np
+        from helpers import to_tensor, to_words
+        from lmserve_b200 import workloads as W
+        from lmserve_b200.kv_worker import KVWorker
+        shape = W.SHAPES["llama31_70b_tp8"].scaled(num_layers=4, num_blocks=64)
+        words = W.normal_words(np.random.default_rng(seed), shape.cache_shape, shape.dtype)
+        cache = to_tensor(words, shape.dtype, "cuda:0")
+        w = KVWorker("decode0", cache)
+        ok = w.pull_kv("prefill0", desc_bytes, local_blocks)
+        w.push_stream.synchronize()
+        got = to_words(cache)
+        w.close()
+        q.put(("ok", ok, got))
+    except Exception as e:  # pragma: no cover - reported to the parent
+        q.put(("error", repr(e), None))
+
+
+def test_pull_kv_from_another_process():
+    shape = W.SHAPES["llama31_70b_tp8"].scaled(num_layers=4, num_blocks=64)
+    src_words, src = make_gpu_cache(shape, 85)
+    prefill = KVWorker("prefill0", src)
+    offered = [11, 12, 50, 3, 4]              # one more than the puller takes
+    local = [20, 21, 22, 63]
+    desc = prefill.get_descriptors(offered)
+    torch.cuda.synchronize()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    p = ctx.Process(target=_puller, args=(desc, 86, local, q))
+    p.start()
+    status, ok, got = q.get(timeout=300)
+    p.join(timeout=60)
+    assert status == "ok" and ok is True, ok
+    want = W.normal_words(np.random.default_rng(86), shape.cache_shape, shape.dtype)
+    cache_oracle.transfer(src_words, want, np.stack([offered[:4], local], axis=1))
+    assert np.array_equal(got, want)
+    assert np.array_equal(to_words(src), src_words)
+    prefill.close()
+
+
 def _pusher(desc_bytes, seed, pairs_src, q):
     """Child process = the prefill-side worker: builds its own cache and pushes blocks into the
     parent's cache through the IPC descriptor."""

@@ -59,6 +59,10 @@ class RecordingWorker:
         self.calls.append(("push_kv", peer_name, bytes(descs), list(block_ids)))
         return len(block_ids) <= 3
 
+    def pull_kv(self, peer_name, descs, block_ids):
+        self.calls.append(("pull_kv", peer_name, bytes(descs), list(block_ids)))
+        return bytes(descs) == b"good"
+
 
 def test_service_over_unix_socket_with_recording_worker():
     worker = RecordingWorker()
@@ -83,6 +87,7 @@ def test_service_over_unix_socket_with_recording_worker():
                 assert stub.PushKV(S.PushKVRequest(peer_name="p", kv_descs=b"x", block_ids=[1, 2])).success is True
                 assert stub.PushKV(S.PushKVRequest(peer_name="p", kv_descs=b"x", block_ids=[1, 2, 3, 4])).success is False
                 assert stub.PullKV(S.PullKVRequest(peer_name="p")).success is False
+                assert stub.PullKV(S.PullKVRequest(peer_name="p", descs=b"good", block_ids=[8])).success is True
                 assert stub.GetLocalAgentMetadata(S.Empty()).agent_name == "kv-test"
                 assert stub.AddRemoteAgentMetadata(S.AgentMetadata(agent_name="peer7")).peer_name == "peer7"
         finally:
