@@ -309,3 +309,57 @@ def test_push_kv_from_another_process():
     cache_oracle.transfer(src_words, want, np.stack([src_blocks, reserved[:4]], axis=1))
     assert np.array_equal(to_words(dst), want)
     decode.close()
+
+
+@pytest.mark.parametrize("variant", [0, 1, 2, 3])
+def test_chunk_ops_do_not_touch_memory_around_their_buffers(variant):
+    """copy_blocks, swap-in and transfer run on caches that are slices of larger buffers; the
+    guard blocks before and after (and the host pool's neighbours) must come out unchanged,
+    including when the first and the last block of the cache are destinations."""
+    lib = _lib.lib()
+    for key in (_lib.TUNE_COPY_VARIANT, _lib.TUNE_XFER_VARIANT, _lib.TUNE_SWAP_VARIANT):
+        lib.lms_set_tuning(key, variant)
+    L_, NB, chunk_words, G = 3, 10, 2064, 2            # 4128-byte chunks
+    rng = np.random.default_rng(88)
+
+    def guarded():
+        words = rng.integers(0, 2**16, size=(L_, NB + 2 * G, chunk_words), dtype=np.uint16)
+        big = to_tensor(words, "fp16", DEV)
+        return words, big, big[:, G:G + NB]
+
+    words, big, kv = guarded()
+    pairs = np.array([[4, 0], [4, NB - 1], [5, 3]], dtype=np.int64)
+    cache_ops.copy_blocks(kv, pairs)
+    want = words.copy()
+    cache_oracle.copy_blocks(want[:, G:G + NB], pairs)
+    torch.cuda.synchronize()
+    assert np.array_equal(to_words(big), want)
+
+    pool = HostPool(6, L_, chunk_words * 2)
+    try:
+        pool.array[...] = rng.integers(0, 256, size=pool.array.shape, dtype=np.uint8)
+        host_before = pool.array.copy()
+        in_pairs = np.array([[2, 0], [5, NB - 1]], dtype=np.int64)
+        cache_ops.swap_blocks(kv, pool, in_pairs, "in")
+        cache_oracle.swap_in(want[:, G:G + NB], host_before.view(np.uint16), in_pairs)
+        torch.cuda.synchronize()
+        assert np.array_equal(to_words(big), want)
+        assert np.array_equal(pool.array, host_before)
+        out_pairs = np.array([[0, 1], [NB - 1, 4]], dtype=np.int64)
+        cache_ops.swap_blocks(kv, pool, out_pairs, "out")
+        torch.cuda.synchronize()
+        host_want = host_before.copy().view(np.uint16)
+        cache_oracle.swap_out(want[:, G:G + NB], host_want, out_pairs)
+        assert np.array_equal(pool.array.view(np.uint16), host_want)
+        assert np.array_equal(to_words(big), want)
+    finally:
+        pool.close()
+
+    dwords, dbig, dst = guarded()
+    tp = np.array([[NB - 1, 0], [0, NB - 1], [3, 5]], dtype=np.int64)
+    cache_ops.transfer_blocks(kv, dst, tp)
+    dwant = dwords.copy()
+    cache_oracle.transfer(want[:, G:G + NB], dwant[:, G:G + NB], tp)
+    torch.cuda.synchronize()
+    assert np.array_equal(to_words(dbig), dwant)
+    assert np.array_equal(to_words(big), want)
