@@ -548,3 +548,43 @@ def test_back_to_back_writes_to_the_same_slots_land_in_stream_order(pdl):
         torch.cuda.synchronize()
         assert torch.equal(kv[:, blk, 0, ent].view(torch.int16), keys[last].view(torch.int16)), trial
         assert torch.equal(kv[:, blk, 1, ent].view(torch.int16), vals[last].view(torch.int16)), trial
+
+
+def test_attention_backend_reads_the_cache_we_wrote():
+    """The consumer of the cache in LMServe is flashinfer's paged attention
+    (models/layers/attention.py:87-106).  Fill a paged cache through this library, run
+    flashinfer's batch decode over it, and compare with attention computed from the dense K/V:
+    the layout and the addressing are what the reference's attention backend expects."""
+    flashinfer = pytest.importorskip("flashinfer")
+    torch.manual_seed(0)
+    NH, NKV, HD, BS, NB, B = 32, 8, 128, 16, 256, 5
+    ctx = np.array([17, 33, 1, 64, 100])          # cached tokens per sequence (the last one is new)
+    bt = W.deal_block_tables(np.random.default_rng(0), NB, (ctx + BS) // BS)
+    indptr, indices = W.paged_metadata(bt.tables)
+    dev = lambda a: torch.from_numpy(a).to(DEV)
+    kv = torch.zeros(NB, 2, BS, NKV, HD, dtype=torch.bfloat16, device=DEV)
+    dense_k = [torch.randn(c + 1, NKV, HD, device=DEV).to(torch.bfloat16) for c in ctx]
+    dense_v = [torch.randn(c + 1, NKV, HD, device=DEV).to(torch.bfloat16) for c in ctx]
+    batch = dev(np.repeat(np.arange(B), ctx + 1).astype(np.int32))
+    pos = dev(np.concatenate([np.arange(c + 1) for c in ctx]).astype(np.int32))
+    last = dev((ctx % BS + 1).astype(np.int32))
+    cache_ops.append_paged_kv_cache(torch.cat(dense_k), torch.cat(dense_v), batch, pos, kv,
+                                    dev(indices), dev(indptr), last)
+    q = torch.randn(B, NH, HD, device=DEV).to(torch.bfloat16)
+    try:
+        ws = torch.empty(128 << 20, dtype=torch.uint8, device=DEV)
+        wrapper = flashinfer.BatchDecodeWithPagedKVCacheWrapper(ws, "NHD")
+        wrapper.plan(dev(indptr), dev(indices), last, NH, NKV, HD, BS,
+                     q_data_type=torch.bfloat16, kv_data_type=torch.bfloat16)
+        out = wrapper.run(q, kv)
+        torch.cuda.synchronize()
+    except Exception as e:  # JIT toolchain missing on the box, API drift, ...
+        pytest.skip(f"flashinfer attention could not run here: {e!r}"[:200])
+    ref = []
+    for b in range(B):
+        k = dense_k[b].float().repeat_interleave(NH // NKV, dim=1)
+        v = dense_v[b].float().repeat_interleave(NH // NKV, dim=1)
+        p = torch.softmax(torch.einsum("hd,shd->hs", q[b].float(), k) / HD ** 0.5, dim=-1)
+        ref.append(torch.einsum("hs,shd->hd", p, v))
+    # attention itself is flashinfer's arithmetic in bf16: 2e-2 absolute on O(1) values
+    assert torch.allclose(out.float(), torch.stack(ref), atol=2e-2, rtol=2e-2)
