@@ -604,20 +604,23 @@ int lms_swap_blocks(int direction, void* gpu, int64_t gpu_layer_stride,
   char* g = (char*)gpu + (long long)layer_begin * gpu_layer_stride;
   char* h = (char*)host + (long long)layer_begin * host_layer_stride;
   // Pair-major unit order: consecutive units are the layers of one block,
-  // which are adjacent in the block-major host pool.
+  // which are adjacent in the block-major host pool.  Sixteen CTAs: the link, not the GPU,
+  // is the limit (4 CTAs already fill PCIe outbound, 8 inbound), larger grids only take SM
+  // slots from the forward pass the swap overlaps with, and they slow per-layer launches down.
+  constexpr int kSwapCtas = 16;
   if (direction == LMS_SWAP_OUT)
     return chunk_copy(g, gpu_layer_stride, gpu_block_stride, h,
                       host_layer_stride, host_block_stride, chunk_bytes, nl,
                       pairs, n_pairs, num_gpu_blocks, num_host_blocks,
                       /*layer_major=*/0, kWhereSwapOut,
                       tuned_variant(LMS_TUNE_SWAP_VARIANT, 0), 0,
-                      tuned(LMS_TUNE_SWAP_OUT_CTAS, sm_count() * 2), stream);
+                      tuned(LMS_TUNE_SWAP_OUT_CTAS, kSwapCtas), stream);
   return chunk_copy(h, host_layer_stride, host_block_stride, g,
                     gpu_layer_stride, gpu_block_stride, chunk_bytes, nl, pairs,
                     n_pairs, num_host_blocks, num_gpu_blocks,
                     /*layer_major=*/0, kWhereSwapIn,
                     tuned_variant(LMS_TUNE_SWAP_VARIANT, 0), 0,
-                    tuned(LMS_TUNE_SWAP_IN_CTAS, sm_count() * 4), stream);
+                    tuned(LMS_TUNE_SWAP_IN_CTAS, kSwapCtas), stream);
 }
 
 int lms_transfer_blocks(const void* src, int64_t src_layer_stride,
