@@ -536,10 +536,58 @@ def bench_swap(comm, stream, cache_view, dev, args, sampler):
         for e in post:
             e.record(stream)
         pre = [torch.cuda.Event() for _ in range(s.num_layers)]
-        ms_lo = timed(comm, stream, lambda i: worker._swap([w.out_pairs], "out", stream, None, post, 1), 1, 1, sampler)
-        ms_li = timed(comm, stream, lambda i: worker._swap([w.in_pairs], "in", stream, pre, None, 1), 1, 1, sampler)
-        out["swap_per_layer_launches"] = {"launches": s.num_layers, "out_GB/s": nbytes / (ms_lo * 1e-3) / 1e9,
-                                          "in_GB/s": nbytes / (ms_li * 1e-3) / 1e9}
+        per_layer = {"launches": s.num_layers}
+        for engine in ("kernel", "dma"):
+            worker.swap_engine = engine
+            ms_lo = timed(comm, stream, lambda i: worker._swap([w.out_pairs], "out", stream, None, post, 1), 1, 1, sampler)
+            ms_li = timed(comm, stream, lambda i: worker._swap([w.in_pairs], "in", stream, pre, None, 1), 1, 1, sampler)
+            per_layer[engine] = {"out_GB/s": nbytes / (ms_lo * 1e-3) / 1e9, "in_GB/s": nbytes / (ms_li * 1e-3) / 1e9}
+        out["swap_per_layer_launches"] = per_layer
+        # the copy-engine form (no kernel, no SM): one strided DMA per block
+        ms_do = timed(comm, stream, lambda i: cache_ops.swap_blocks(kv, pool, w.out_pairs, "out", engine="dma"), reps, 1, sampler) / reps
+        ms_di = timed(comm, stream, lambda i: cache_ops.swap_blocks(kv, pool, w.in_pairs, "in", engine="dma"), reps, 1, sampler) / reps
+        out["swap_copy_engine"] = {"out_GB/s": nbytes / (ms_do * 1e-3) / 1e9, "in_GB/s": nbytes / (ms_di * 1e-3) / 1e9,
+                                   "dma_copies_per_swap": n_blocks}
+        # what a concurrent swap-out costs a stream of dense GEMMs (the forward pass it overlaps)
+        if not args.small:
+            a = torch.randn(8192, 8192, device=dev, dtype=torch.bfloat16)
+            b = torch.randn(8192, 8192, device=dev, dtype=torch.bfloat16)
+            copy_stream = torch.cuda.Stream()
+
+            def gemms(engine):
+                """150 GEMMs on the main thread and stream; the swap is issued at the same
+                moment from a second host thread on its own stream (as a KV worker would)."""
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                start = threading.Barrier(2)
+
+                def swap():
+                    torch.cuda.set_device(dev)
+                    start.wait()
+                    with torch.cuda.stream(copy_stream):
+                        cache_ops.swap_blocks(kv, pool, w.out_pairs if engine == "dma" else out_pairs,
+                                              "out", engine=engine)
+
+                t = threading.Thread(target=swap if engine else start.wait)
+                t.start()
+                start.wait()
+                e0.record(stream)
+                for _ in range(150):
+                    torch.matmul(a, b)
+                e1.record(stream)
+                t.join()
+                torch.cuda.synchronize()
+                return e0.elapsed_time(e1)
+
+            gemms(None)
+            alone = gemms(None)
+            out["swap_out_overlapping_gemms"] = {
+                "gemm_ms_alone": alone,
+                "gemm_slowdown_with_kernel_swap": gemms("kernel") / alone,
+                "gemm_slowdown_with_copy_engine_swap": gemms("dma") / alone,
+                "note": "150 bf16 GEMMs of 8192^3 on one stream; a 16 GiB swap-out issued at the "
+                        "same time from a second host thread on another stream"}
+            del a, b
         out["swap_pool"] = {"host_blocks": nhb, "host_pool_GiB": pool.nbytes / (1 << 30),
                             "moved_blocks": n_blocks, "pin_seconds": pin_s}
     finally:

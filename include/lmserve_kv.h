@@ -74,7 +74,10 @@ typedef enum lms_status {
                                     with programmatic stream serialization: the grid becomes resident
                                     while the previous kernel drains and still waits for that kernel
                                     before touching memory, so stream order is unchanged; 2 = off */
-#define LMS_TUNE__COUNT 12
+#define LMS_TUNE_SWAP_ENGINE 12  /* lms_swap_blocks_host only: 1 (built-in) = the SM kernel, 2 = the copy
+                                    engines: one strided DMA copy per block (all layers of the range),
+                                    no SM is used, so a concurrent GEMM keeps every SM */
+#define LMS_TUNE__COUNT 13
 
 /* Library version (LMS_VERSION of the build). */
 int lms_version(void);
@@ -308,6 +311,13 @@ int lms_transfer_blocks(const void* src, int64_t src_layer_stride,
  * kernel still reads it.  `host_pairs` may be reused as soon as the call returns when it is
  * pageable memory; page-locked memory must stay valid until `stream` has passed the call.
  * All other arguments are those of the device-table entry points above.
+ *
+ * lms_swap_blocks_host can also run on the copy engines instead of the SMs
+ * (LMS_TUNE_SWAP_ENGINE = 2): one cudaMemcpy2DAsync per block covering the layer range (one
+ * copy per layer and block when the layer stride exceeds the 2D-copy pitch limit).  It is a
+ * little slower on an idle GPU (2 MiB copies instead of one kernel) and needs one driver call
+ * per block, but it leaves every SM to the kernels it overlaps with; with debug checks on, the
+ * block ids are checked on the host and LMS_ERR_INDEX is returned before anything is copied.
  */
 int lms_copy_blocks_host(void* kv, int64_t layer_stride, int64_t block_stride,
                          int64_t chunk_bytes, int32_t num_layers,
@@ -320,6 +330,18 @@ int lms_swap_blocks_host(int direction, void* gpu, int64_t gpu_layer_stride,
                          const int64_t* host_pairs, int64_t n_pairs,
                          int64_t num_gpu_blocks, int64_t num_host_blocks,
                          void* stream);
+/* The copy-engine form of lms_swap_blocks_host as an entry point of its own (what
+ * LMS_TUNE_SWAP_ENGINE = 2 selects): no kernel is launched and no SM is used.  This is the
+ * form to use when the swap overlaps the model's forward pass, as it does in LMServe
+ * (runtime/worker/llm_worker/kv_worker.py:249-295): a resident copy kernel, however small,
+ * keeps full-SM GEMM kernels from using the SMs it sits on.  Same arguments. */
+int lms_swap_blocks_dma(int direction, void* gpu, int64_t gpu_layer_stride,
+                        int64_t gpu_block_stride, void* host,
+                        int64_t host_block_stride, int64_t host_layer_stride,
+                        int64_t chunk_bytes, int32_t layer_begin, int32_t layer_end,
+                        const int64_t* host_pairs, int64_t n_pairs,
+                        int64_t num_gpu_blocks, int64_t num_host_blocks,
+                        void* stream);
 int lms_transfer_blocks_host(const void* src, int64_t src_layer_stride,
                              int64_t src_block_stride, void* dst,
                              int64_t dst_layer_stride, int64_t dst_block_stride,

@@ -36,6 +36,7 @@ TUNE_XFER_VARIANT = 8
 TUNE_WRITE_VPT = 9
 TUNE_SWAP_VARIANT = 10
 TUNE_WRITE_PDL = 11
+TUNE_SWAP_ENGINE = 12
 
 # name -> (restype, argtypes); one entry per declaration in include/lmserve_kv.h
 SIGNATURES = {
@@ -82,6 +83,9 @@ SIGNATURES = {
     "lms_copy_blocks_host_static": (c_int, [
         c_void_p, c_int64, c_int64, c_int64, c_int32, c_void_p, c_int64, c_void_p]),
     "lms_swap_blocks_host": (c_int, [
+        c_int, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64,
+        c_int32, c_int32, c_void_p, c_int64, c_int64, c_int64, c_void_p]),
+    "lms_swap_blocks_dma": (c_int, [
         c_int, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64,
         c_int32, c_int32, c_void_p, c_int64, c_int64, c_int64, c_void_p]),
     "lms_transfer_blocks_host": (c_int, [

@@ -604,10 +604,11 @@ int lms_swap_blocks(int direction, void* gpu, int64_t gpu_layer_stride,
   char* g = (char*)gpu + (long long)layer_begin * gpu_layer_stride;
   char* h = (char*)host + (long long)layer_begin * host_layer_stride;
   // Pair-major unit order: consecutive units are the layers of one block,
-  // which are adjacent in the block-major host pool.  Sixteen CTAs: the link, not the GPU,
-  // is the limit (4 CTAs already fill PCIe outbound, 8 inbound), larger grids only take SM
-  // slots from the forward pass the swap overlaps with, and they slow per-layer launches down.
-  constexpr int kSwapCtas = 16;
+  // which are adjacent in the block-major host pool.  Eight CTAs: the link, not the GPU, is
+  // the limit (4 CTAs already fill PCIe outbound, 8 inbound).  A resident copy CTA takes its
+  // SM away from full-SM GEMM kernels that run at the same time, so larger grids only cost
+  // the forward pass the swap overlaps with, and they slow per-layer launches down.
+  constexpr int kSwapCtas = 8;
   if (direction == LMS_SWAP_OUT)
     return chunk_copy(g, gpu_layer_stride, gpu_block_stride, h,
                       host_layer_stride, host_block_stride, chunk_bytes, nl,
@@ -686,6 +687,85 @@ int lms_copy_blocks_host_static(void* kv, int64_t layer_stride, int64_t block_st
   return LMS_OK;
 }
 
+#pragma GCC visibility pop
+}  // extern "C"
+
+namespace {
+
+// Swap on the copy engines: one strided DMA per block over the layer range.
+int swap_blocks_dma(int direction, char* gpu, int64_t gpu_layer_stride,
+                    int64_t gpu_block_stride, char* host, int64_t host_block_stride,
+                    int64_t host_layer_stride, int64_t chunk_bytes, int32_t layer_begin,
+                    int32_t layer_end, const int64_t* pairs, int64_t n_pairs,
+                    int64_t num_gpu_blocks, int64_t num_host_blocks, cudaStream_t stream) {
+  if (direction != LMS_SWAP_OUT && direction != LMS_SWAP_IN) return LMS_ERR_RANGE;
+  if (layer_begin < 0 || layer_end < layer_begin || n_pairs < 0 || chunk_bytes <= 0)
+    return LMS_ERR_RANGE;
+  const int nl = layer_end - layer_begin;
+  if (n_pairs == 0 || nl == 0) return LMS_OK;
+  if (!gpu || !host || !pairs) return LMS_ERR_NULL;
+  if (!mult16(gpu_layer_stride) || !mult16(gpu_block_stride) || !mult16(host_block_stride) ||
+      !mult16(host_layer_stride) || !mult16(chunk_bytes) || !ptr16(gpu) || !ptr16(host))
+    return LMS_ERR_ALIGN;
+  const bool out = direction == LMS_SWAP_OUT;
+  if (g_checks.load(std::memory_order_relaxed)) {
+    for (int64_t i = 0; i < n_pairs; ++i) {
+      const int64_t g = out ? pairs[2 * i] : pairs[2 * i + 1];
+      const int64_t h = out ? pairs[2 * i + 1] : pairs[2 * i];
+      if (g < 0 || h < 0 || (num_gpu_blocks > 0 && g >= num_gpu_blocks) ||
+          (num_host_blocks > 0 && h >= num_host_blocks)) {
+        snprintf(g_cuda_msg, sizeof(g_cuda_msg), "block pair %lld (%lld, %lld) is out of range",
+                 (long long)i, (long long)pairs[2 * i], (long long)pairs[2 * i + 1]);
+        return LMS_ERR_INDEX;
+      }
+    }
+  }
+  int dev = 0, max_pitch = 0;
+  LMS_CUDA(cudaGetDevice(&dev));
+  LMS_CUDA(cudaDeviceGetAttribute(&max_pitch, cudaDevAttrMaxPitch, dev));
+  const bool strided = gpu_layer_stride <= max_pitch && host_layer_stride <= max_pitch;
+  const cudaMemcpyKind kind = out ? cudaMemcpyDeviceToHost : cudaMemcpyHostToDevice;
+  for (int64_t i = 0; i < n_pairs; ++i) {
+    const int64_t gb = out ? pairs[2 * i] : pairs[2 * i + 1];
+    const int64_t hb = out ? pairs[2 * i + 1] : pairs[2 * i];
+    char* g = gpu + (long long)layer_begin * gpu_layer_stride + gb * gpu_block_stride;
+    char* h = host + hb * host_block_stride + (long long)layer_begin * host_layer_stride;
+    if (strided) {
+      if (out)
+        LMS_CUDA(cudaMemcpy2DAsync(h, (size_t)host_layer_stride, g, (size_t)gpu_layer_stride,
+                                   (size_t)chunk_bytes, (size_t)nl, kind, stream));
+      else
+        LMS_CUDA(cudaMemcpy2DAsync(g, (size_t)gpu_layer_stride, h, (size_t)host_layer_stride,
+                                   (size_t)chunk_bytes, (size_t)nl, kind, stream));
+    } else {
+      for (int l = 0; l < nl; ++l) {
+        char* gl = g + (long long)l * gpu_layer_stride;
+        char* hl = h + (long long)l * host_layer_stride;
+        LMS_CUDA(cudaMemcpyAsync(out ? hl : gl, out ? gl : hl, (size_t)chunk_bytes, kind, stream));
+      }
+    }
+  }
+  return LMS_OK;
+}
+
+}  // namespace
+
+extern "C" {
+#pragma GCC visibility push(default)
+
+int lms_swap_blocks_dma(int direction, void* gpu, int64_t gpu_layer_stride,
+                        int64_t gpu_block_stride, void* host,
+                        int64_t host_block_stride, int64_t host_layer_stride,
+                        int64_t chunk_bytes, int32_t layer_begin, int32_t layer_end,
+                        const int64_t* host_pairs, int64_t n_pairs,
+                        int64_t num_gpu_blocks, int64_t num_host_blocks,
+                        void* stream) {
+  return swap_blocks_dma(direction, (char*)gpu, gpu_layer_stride, gpu_block_stride,
+                         (char*)host, host_block_stride, host_layer_stride, chunk_bytes,
+                         layer_begin, layer_end, host_pairs, n_pairs, num_gpu_blocks,
+                         num_host_blocks, (cudaStream_t)stream);
+}
+
 int lms_swap_blocks_host(int direction, void* gpu, int64_t gpu_layer_stride,
                          int64_t gpu_block_stride, void* host,
                          int64_t host_block_stride, int64_t host_layer_stride,
@@ -693,6 +773,11 @@ int lms_swap_blocks_host(int direction, void* gpu, int64_t gpu_layer_stride,
                          const int64_t* host_pairs, int64_t n_pairs,
                          int64_t num_gpu_blocks, int64_t num_host_blocks,
                          void* stream) {
+  if (tuned(LMS_TUNE_SWAP_ENGINE, 1) == 2)
+    return swap_blocks_dma(direction, (char*)gpu, gpu_layer_stride, gpu_block_stride,
+                           (char*)host, host_block_stride, host_layer_stride, chunk_bytes,
+                           layer_begin, layer_end, host_pairs, n_pairs, num_gpu_blocks,
+                           num_host_blocks, (cudaStream_t)stream);
   return with_host_table(host_pairs, n_pairs, stream, [&](const int64_t* pairs) {
     return lms_swap_blocks(direction, gpu, gpu_layer_stride, gpu_block_stride, host,
                            host_block_stride, host_layer_stride, chunk_bytes,

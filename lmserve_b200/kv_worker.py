@@ -223,8 +223,16 @@ class KVWorker:
     tensor (or its ``[L, num_gpu_blocks, chunk]`` view); the worker does not own it.
     """
 
-    def __init__(self, name: str, gpu_kv_caches: torch.Tensor, num_host_blocks: int = 0):
+    def __init__(self, name: str, gpu_kv_caches: torch.Tensor, num_host_blocks: int = 0,
+                 swap_engine: str = "kernel"):
         cache_ops._require_cuda("gpu_kv_caches", gpu_kv_caches)
+        if swap_engine not in ("kernel", "dma"):
+            raise ValueError("swap_engine must be 'kernel' or 'dma'")
+        # "kernel": the sm_100a gather/scatter kernel on 16 CTAs - full PCIe rate even when
+        # launched once per layer, but a resident kernel costs concurrent full-SM GEMMs 10-90 %.
+        # "dma": copy engines only, no SM is touched; full rate needs many layers per launch
+        # (one 64 KiB copy per layer and block, the reference's pattern, reaches 13 GB/s).
+        self.swap_engine = swap_engine
         self.name = name
         self.gpu_kv_caches = gpu_kv_caches
         self.device = gpu_kv_caches.device
@@ -293,9 +301,12 @@ class KVWorker:
         events = pre_events if pre_events is not None else post_events
         L = self.num_layers
         with torch.cuda.device(self.device), torch.cuda.stream(stream):
-            pairs = cache_ops._pairs_on_device(pairs_np, self.device)
+            engine = self.swap_engine
+            # the kernel reads the table on the device (uploaded once for all layer launches);
+            # the copy engines are driven from the host table
+            pairs = pairs_np if engine == "dma" else cache_ops._pairs_on_device(pairs_np, self.device)
             if events is None:
-                cache_ops.swap_blocks(self.gpu_kv_caches, self.host_pool, pairs, direction)
+                cache_ops.swap_blocks(self.gpu_kv_caches, self.host_pool, pairs, direction, engine=engine)
                 return
             step = max(1, int(group or 1))
             for l0 in range(0, L, step):
@@ -304,7 +315,7 @@ class KVWorker:
                     for l in range(l0, l1):
                         stream.wait_event(post_events[l])
                 cache_ops.swap_blocks(self.gpu_kv_caches, self.host_pool, pairs, direction,
-                                      layers=(l0, l1))
+                                      layers=(l0, l1), engine=engine)
                 if pre_events is not None:
                     for l in range(l0, l1):
                         pre_events[l].record(stream)

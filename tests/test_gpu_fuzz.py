@@ -17,7 +17,7 @@ DEV = "cuda:0"
 @pytest.fixture(autouse=True)
 def _reset_tuning():
     yield
-    for key in range(1, 12):
+    for key in range(1, 13):
         _lib.lib().lms_set_tuning(key, -1)
 
 

@@ -25,7 +25,7 @@ VARIANTS = [0, 1, 2, 3, 4]  # tiled 16/32-byte vectors, bulk (TMA) copies, until
 def _reset_tuning():
     yield
     L = _lib.lib()
-    for key in range(1, 12):
+    for key in range(1, 13):
         L.lms_set_tuning(key, -1)
     L.lms_set_debug_checks(0)
 

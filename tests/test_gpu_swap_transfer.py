@@ -20,7 +20,7 @@ DEV = "cuda:0"
 @pytest.fixture(autouse=True)
 def _reset_tuning():
     yield
-    for key in range(1, 12):
+    for key in range(1, 13):
         _lib.lib().lms_set_tuning(key, -1)
 
 
@@ -58,6 +58,53 @@ def test_swap_out_in_vs_oracle(ctas, variant):
         back = {int(h): int(g) for g, h in sw.out_pairs}
         for h, d in sw.in_pairs:
             assert np.array_equal(got[:, d], got[:, back[int(h)]])
+    finally:
+        pool.close()
+
+
+@pytest.mark.parametrize("big_stride", [False, True])
+def test_swap_on_the_copy_engines(big_stride):
+    """LMS_TUNE_SWAP_ENGINE = 2: the same swap issued as strided DMA copies (one per block), or
+    as one copy per layer and block when the layer stride is beyond the 2D-copy pitch limit;
+    host-side index check under debug checks."""
+    lib = _lib.lib()
+    lib.lms_set_tuning(_lib.TUNE_SWAP_ENGINE, 2)
+    L_, NB, chunk_words = 3, 24, 4096
+    rng = np.random.default_rng(90)
+    words = rng.integers(0, 2**16, size=(L_, NB, chunk_words), dtype=np.uint16)
+    if big_stride:   # layers 2.25 GiB apart inside one buffer: pitch > 2^31 - 1
+        far = 9 * (1 << 27)                                   # elements
+        buf = torch.zeros(2 * far + NB * chunk_words + 64, dtype=torch.float16, device=DEV)
+        gpu = torch.as_strided(buf, (L_, NB, chunk_words), (far, chunk_words, 1))
+        gpu.copy_(to_tensor(words, "fp16", DEV))
+    else:
+        gpu = to_tensor(words, "fp16", DEV)
+    pool = HostPool(10, L_, chunk_words * 2)
+    try:
+        pool.array[...] = 0
+        out_pairs = np.array([[3, 9], [23, 0], [7, 4]], dtype=np.int64)
+        before = lib.lms_launch_count()
+        cache_ops.swap_blocks(gpu, pool, out_pairs, "out", layers=(1, 3))
+        torch.cuda.synchronize()
+        assert lib.lms_launch_count() == before            # no kernel of ours was launched
+        host_want = np.zeros((10, L_, chunk_words), np.uint16)
+        gpu_want = words.copy()
+        cache_oracle.swap_out(gpu_want, host_want, out_pairs, layers=(1, 3))
+        assert np.array_equal(pool.array.view(np.uint16), host_want)
+        in_pairs = np.array([[9, 10], [4, 11]], dtype=np.int64)
+        cache_ops.swap_blocks(gpu, pool, in_pairs, "in")
+        torch.cuda.synchronize()
+        cache_oracle.swap_in(gpu_want, host_want, in_pairs)
+        assert np.array_equal(to_words(gpu.contiguous()), gpu_want)
+        lib.lms_set_debug_checks(1)
+        try:
+            with pytest.raises(_lib.LmsError) as e:
+                cache_ops.swap_blocks(gpu, pool, np.array([[3, 1], [2, 77]], dtype=np.int64), "out")
+            assert e.value.status == _lib.LMS_ERR_INDEX
+        finally:
+            lib.lms_set_debug_checks(0)
+        torch.cuda.synchronize()
+        assert np.array_equal(pool.array.view(np.uint16), host_want)   # nothing was copied
     finally:
         pool.close()
 
