@@ -323,7 +323,7 @@ def run_ours(args):
 
         # ------------------------------------------------------------- other workloads
         if args.small:
-            ops_wanted = ops_wanted & {"prefill_cow", "swap", "rope", "transfer_local"}
+            ops_wanted = ops_wanted & {"prefill_cow", "swap", "rope", "transfer_local", "index_prep"}
 
         def extra(names, fn):
             """Runs one of the other workloads; a failure there (a pool that does not fit, no
@@ -343,6 +343,7 @@ def run_ours(args):
                                                              sampler, args.small))
             extra(["swap"], lambda: bench_swap(comm, stream, cache_view, dev, args, sampler))
             extra(["rope"], lambda: bench_rope_fusion(comm, stream, cache_view, dev, args, sampler))
+            extra(["index_prep"], lambda: bench_index_prep(comm, stream, dev, args, sampler))
             if torch.cuda.device_count() >= 2 and "transfer_local" in ops_wanted:
                 extra(["transfer_local"], lambda: bench_transfer_local(comm, stream, cache_view, dev,
                                                                        args, sampler))
@@ -654,6 +655,88 @@ def bench_rope_fusion(comm, stream, cache_view, dev, args, sampler):
     return out
 
 
+def bench_index_prep(comm, stream, dev, args, sampler):
+    """Per-step index preparation, host wall time per step with a synchronize at the end (the
+    forward pass cannot start before its indices exist): LMServe's way — Python lists, one
+    torch.tensor(...).to('cuda') per array and flashinfer's two helpers
+    (model_worker.py:310-433), restated here as the baseline — against one packed upload and one
+    kernel (StepInputBuilder).  Same request objects, seeded; a decode step of 256 requests and
+    a chunked-prefill step of 64 x 512 tokens."""
+    import copy
+    import time
+    from lmserve_b200.step_inputs import StepInputBuilder
+    try:
+        import flashinfer
+    except Exception:  # noqa: BLE001
+        flashinfer = None
+
+    def reference_way(inputs, page_size=16):
+        flatten_input_ids, position_ids, seqlens_q = [], [], []
+        inputs.sort(key=lambda x: -x.input_len)
+        for data in inputs:
+            flatten_input_ids += data.input_ids
+            position_ids += [i for i in range(data.filled_token_len, data.context_len)]
+            seqlens_q.append(data.input_len)
+        ids = torch.tensor(flatten_input_ids, dtype=torch.long).to(dev, non_blocking=True)
+        pos_ids = torch.tensor(position_ids, dtype=torch.int).to(dev, non_blocking=True)
+        cu_q = torch.tensor(np.cumsum([0] + seqlens_q), dtype=torch.int).to(dev, non_blocking=True)
+        kv_block_indices, num_blocks_per_seqs, kv_last_block_lens = [], [], []
+        for data in inputs:
+            kv_block_indices += data.block_ids
+            num_blocks_per_seqs.append(len(data.block_ids))
+            kv_last_block_lens.append((data.context_len - 1) % page_size + 1)
+        indptr = torch.tensor(np.cumsum([0] + num_blocks_per_seqs), dtype=torch.int).to(dev, non_blocking=True)
+        indices = torch.tensor(kv_block_indices, dtype=torch.int).to(dev, non_blocking=True)
+        last = torch.tensor(kv_last_block_lens, dtype=torch.int).to(dev, non_blocking=True)
+        nnz = sum(seqlens_q)
+        if flashinfer is not None:
+            b, p = flashinfer.get_batch_indices_positions(
+                cu_q, flashinfer.get_seq_lens(indptr, last, page_size), nnz)
+        else:
+            seq = torch.clamp(indptr[1:] - indptr[:-1] - 1, min=0) * page_size + last
+            q = cu_q[1:] - cu_q[:-1]
+            b = torch.repeat_interleave(torch.arange(len(inputs), device=dev, dtype=torch.int), q.long())
+            p = (torch.arange(nnz, device=dev, dtype=torch.int) - cu_q[b.long()] + (seq - q)[b.long()]).int()
+        return ids, pos_ids, cu_q, indptr, indices, last, b, p
+
+    cases = {
+        "decode_256_requests": dict(num_decode=256, ctx_lo=128, ctx_hi=4096, num_prefill=0,
+                                    chunk_tokens=0, max_offset=0),
+        "prefill_64x512_tokens": dict(num_decode=0, ctx_lo=0, ctx_hi=0, num_prefill=64,
+                                      chunk_tokens=512, max_offset=8192),
+    }
+    builder = StepInputBuilder(dev, 16, max_batch=256, max_tokens=32768, max_blocks=131072)
+    out = {"flashinfer_helpers": flashinfer is not None}
+    for name, kw in cases.items():
+        reqs = [W.make_step_requests(65536, 16, seed=6000 + i, **kw) for i in range(4)]
+        ref = reference_way(copy.copy(reqs[0]))
+        ids, s = builder.make_inputs(copy.copy(reqs[0]))
+        torch.cuda.synchronize()
+        same = (torch.equal(ref[0], ids) and torch.equal(ref[1], s.position_ids)
+                and torch.equal(ref[2], s.cu_seqlens_q) and torch.equal(ref[3], s.kv_block_indptrs)
+                and torch.equal(ref[4], s.kv_block_indices) and torch.equal(ref[5], s.kv_last_block_lens)
+                and torch.equal(ref[6], s.batch_indices) and torch.equal(ref[7], s.positions))
+        res = {"results_match": bool(same), "tokens": int(ids.numel()),
+               "block_table_entries": int(s.kv_block_indices.numel())}
+        for label, fn in (("reference_way_us", reference_way), ("one_upload_one_kernel_us", builder.make_inputs)):
+            times = []
+            for i in range(23):
+                r = copy.copy(reqs[i % 4])
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                fn(r)
+                torch.cuda.synchronize()
+                times.append(time.perf_counter() - t0)
+            res[label] = float(np.median(times[3:])) * 1e6
+        # the device part alone: the kernel re-run on the uploaded buffer
+        T, NB, B = int(ids.numel()), int(s.kv_block_indices.numel()), len(reqs[0])
+        builder.make_inputs(copy.copy(reqs[0]))
+        ms = timed(comm, stream, lambda i: builder._launch(B, T, NB, 0, 0, 0), 50, 3, sampler) / 50
+        res["kernel_us"] = ms * 1e3
+        out[name] = res
+    return {"index_prep": out}
+
+
 def bench_vs_flashinfer(comm, stream, cache_view, dev, args, sampler):
     """The decode step's 32 per-layer cache writes through flashinfer.append_paged_kv_cache (the
     call LMServe makes, models/layers/attention.py:76-85) and through this library, eager and
@@ -931,7 +1014,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--ops", default="all",
-                    help="comma list of extra workloads: all, none, prefill_cow, swap, rope, tp8, "
+                    help="comma list of extra workloads: all, none, prefill_cow, swap, rope, index_prep, tp8, "
                          "transfer (multi-rank), transfer_local (two GPUs in one process; not in 'all'), "
                          "flashinfer (comparison with flashinfer.append_paged_kv_cache; not in 'all')")
     ap.add_argument("--host-pool-gib", type=float, default=32.0,

@@ -62,7 +62,8 @@ typedef enum lms_status {
                                     3 = untiled one-vector-per-thread 32-byte, 4 = untiled 16-byte */
 #define LMS_TUNE_WRITE_TILE_BYTES 2 /* payload bytes read per CTA of the cache write */
 #define LMS_TUNE_COPY_VARIANT 3  /* 0 = persistent 16-byte ld/st, 1 = persistent 32-byte, 2 = bulk-copy (TMA),
-                                    3 = untiled one-vector-per-thread */
+                                    3 = untiled one-vector-per-thread, 4 = persistent 16-byte with
+                                    1024-thread CTAs (128 KiB in flight per CTA, for grids of a few CTAs) */
 #define LMS_TUNE_COPY_CTAS_PER_SM 4
 #define LMS_TUNE_SWAP_OUT_CTAS 5 /* total CTAs of the GPU->host kernel */
 #define LMS_TUNE_SWAP_IN_CTAS 6  /* total CTAs of the host->GPU kernel */
@@ -207,6 +208,41 @@ int lms_append_paged_kv_cache(const void* key, const void* value,
                               const int32_t* kv_indptr, int64_t num_tokens,
                               int32_t num_layers, int64_t row_bytes,
                               int32_t block_size, int64_t num_blocks, void* stream);
+
+/*
+ * Per-step index preparation on the device — replaces the host-side list building and the ten
+ * separate uploads of
+ *   ModelWorker._make_inputs      runtime/worker/llm_worker/model_worker.py:310-433
+ * including its calls of flashinfer.get_seq_lens and flashinfer.get_batch_indices_positions
+ * (model_worker.py:425-433).  The caller sorts the requests as the reference does (descending
+ * input_len, model_worker.py:328) and uploads, per request b: input_len[b] (new tokens),
+ * filled_len[b] (InferInput.filled_token_len), context_len[b], num_blocks[b] =
+ * len(InferInput.block_ids); the block tables concatenated in block_ids[total_blocks]; and
+ * optionally the new token ids in token_ids[total_tokens].  All pointers are device pointers
+ * (int32, slot_mapping / input_ids int64); any output may be NULL.  One launch writes
+ *   cu_seqlens_q[batch+1], kv_block_indptrs[batch+1]   exclusive prefix sums
+ *   kv_last_block_lens[b] = (context_len[b]-1) mod block_size + 1      (floor modulo, as Python)
+ *   kv_block_indices      = block_ids
+ *   position_ids[i]       = filled_len[b] + off          for token i = cu_seqlens_q[b] + off
+ *   batch_indices[i] = b, positions[i] = seq_len[b] - input_len[b] + off with
+ *                         seq_len[b] = max(num_blocks[b]-1, 0)*block_size + kv_last_block_lens[b]
+ *   slot_mapping[i]       = block_ids[kv_block_indptrs[b] + positions[i]/block_size]*block_size
+ *                           + positions[i] % block_size, or -1 when that page is not in the
+ *                           request's table (reported as LMS_ERR_INDEX with debug checks on)
+ *   input_ids[i]          = token_ids[i] widened to int64
+ * total_tokens must equal the sum of input_len and total_blocks the sum of num_blocks.
+ * batch <= LMS_STEP_MAX_BATCH, else LMS_ERR_TOO_LARGE.
+ */
+#define LMS_STEP_MAX_BATCH 4096
+int lms_build_step_indices(const int32_t* input_len, const int32_t* filled_len,
+                           const int32_t* context_len, const int32_t* num_blocks,
+                           const int32_t* block_ids, const int32_t* token_ids,
+                           int32_t batch, int64_t total_tokens, int64_t total_blocks,
+                           int32_t block_size, int32_t* position_ids,
+                           int32_t* cu_seqlens_q, int32_t* kv_block_indptrs,
+                           int32_t* kv_block_indices, int32_t* kv_last_block_lens,
+                           int32_t* batch_indices, int32_t* positions,
+                           int64_t* slot_mapping, int64_t* input_ids, void* stream);
 
 /*
  * Rotary position embedding, optionally fused with the cache write that follows it in the

@@ -19,7 +19,7 @@ PKG_DIR = Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 LIB_NAME = "liblmserve_kv.so"
 LIB_PATH = PKG_DIR / LIB_NAME
-SOURCES = ["capi.cu", "write_rows.cu", "chunk_copy.cu", "rope_cache.cu"]
+SOURCES = ["capi.cu", "write_rows.cu", "chunk_copy.cu", "rope_cache.cu", "step_indices.cu"]
 HEADERS = ["kv_common.cuh", "kernels.cuh"]
 PUBLIC_HEADER = PKG_DIR.parent / "include" / "lmserve_kv.h"
 

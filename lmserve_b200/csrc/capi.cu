@@ -363,7 +363,7 @@ int lms_set_tuning(int key, int value) {
   const bool is_variant = key == LMS_TUNE_WRITE_VARIANT || key == LMS_TUNE_COPY_VARIANT ||
                           key == LMS_TUNE_XFER_VARIANT || key == LMS_TUNE_SWAP_VARIANT;
   if (is_variant) {
-    if (value > (key == LMS_TUNE_WRITE_VARIANT ? 4 : 3)) return LMS_ERR_RANGE;
+    if (value > 4) return LMS_ERR_RANGE;
     g_tuning[key].store(value < 0 ? 0 : value + 1);
   } else {
     g_tuning[key].store(value < 0 ? 0 : value);
@@ -398,6 +398,11 @@ int lms_check_device_errors(void* stream, int64_t* index, int64_t* value) {
   LMS_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
   if (index) *index = h.index;
   if (value) *value = h.value;
+  if (h.code == kErrBadPosition && h.where == kWhereStepIndices) {
+    snprintf(g_cuda_msg, sizeof(g_cuda_msg),
+             "token %lld: position %lld has no page in its request's block table", h.index, h.value);
+    return LMS_ERR_INDEX;
+  }
   if (h.code == kErrBadPosition) {
     snprintf(g_cuda_msg, sizeof(g_cuda_msg), "position %lld of token %lld is outside the cos/sin cache",
              h.value, h.index);
@@ -576,6 +581,61 @@ int lms_rope_and_cache(const void* query, const void* key, const void* value,
   return LMS_OK;
 }
 
+int lms_build_step_indices(const int32_t* input_len, const int32_t* filled_len,
+                           const int32_t* context_len, const int32_t* num_blocks,
+                           const int32_t* block_ids, const int32_t* token_ids,
+                           int32_t batch, int64_t total_tokens, int64_t total_blocks,
+                           int32_t block_size, int32_t* position_ids,
+                           int32_t* cu_seqlens_q, int32_t* kv_block_indptrs,
+                           int32_t* kv_block_indices, int32_t* kv_last_block_lens,
+                           int32_t* batch_indices, int32_t* positions,
+                           int64_t* slot_mapping, int64_t* input_ids, void* stream) {
+  if (batch < 0 || total_tokens < 0 || total_blocks < 0 || block_size <= 0 ||
+      total_tokens > 0x7fffffffll || total_blocks > 0x7fffffffll)
+    return LMS_ERR_RANGE;
+  if (batch > LMS_STEP_MAX_BATCH) return LMS_ERR_TOO_LARGE;
+  // An empty step still defines cu_seqlens_q[0] = kv_block_indptrs[0] = 0.
+  if (batch == 0 && total_tokens == 0 && total_blocks == 0 && !cu_seqlens_q && !kv_block_indptrs)
+    return LMS_OK;
+  if (batch > 0 && (!input_len || !filled_len || !context_len || !num_blocks)) return LMS_ERR_NULL;
+  if (total_blocks > 0 && !block_ids) return LMS_ERR_NULL;
+  if (input_ids && total_tokens > 0 && !token_ids) return LMS_ERR_NULL;
+  const void* four[] = {input_len, filled_len, context_len, num_blocks, block_ids, token_ids,
+                        position_ids, cu_seqlens_q, kv_block_indptrs, kv_block_indices,
+                        kv_last_block_lens, batch_indices, positions};
+  for (const void* q : four)
+    if (((uintptr_t)q & 3u) != 0) return LMS_ERR_ALIGN;
+  if (((uintptr_t)slot_mapping & 7u) != 0 || ((uintptr_t)input_ids & 7u) != 0) return LMS_ERR_ALIGN;
+
+  DeviceState* ds = nullptr;
+  if (int rc = device_state(&ds)) return rc;
+  StepIndexParams p{};
+  p.input_len = input_len;
+  p.filled_len = filled_len;
+  p.context_len = context_len;
+  p.num_blocks = num_blocks;
+  p.block_ids = block_ids;
+  p.token_ids = token_ids;
+  p.batch = batch;
+  p.block_size = block_size;
+  p.total_tokens = total_tokens;
+  p.total_blocks = total_blocks;
+  p.position_ids = position_ids;
+  p.cu_seqlens_q = cu_seqlens_q;
+  p.kv_block_indptrs = kv_block_indptrs;
+  p.kv_block_indices = kv_block_indices;
+  p.kv_last_block_lens = kv_last_block_lens;
+  p.batch_indices = batch_indices;
+  p.positions = positions;
+  p.slot_mapping = (long long*)slot_mapping;
+  p.input_ids = (long long*)input_ids;
+  p.err = ds->err.load(std::memory_order_relaxed);
+  p.checks = g_checks.load(std::memory_order_relaxed);
+  LMS_CUDA(launch_step_indices(p, ds->sms, (cudaStream_t)stream));
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return LMS_OK;
+}
+
 int lms_copy_blocks(void* kv, int64_t layer_stride, int64_t block_stride,
                     int64_t chunk_bytes, int32_t num_layers,
                     const int64_t* pairs, int64_t n_pairs, int64_t num_blocks,
@@ -604,23 +664,25 @@ int lms_swap_blocks(int direction, void* gpu, int64_t gpu_layer_stride,
   char* g = (char*)gpu + (long long)layer_begin * gpu_layer_stride;
   char* h = (char*)host + (long long)layer_begin * host_layer_stride;
   // Pair-major unit order: consecutive units are the layers of one block,
-  // which are adjacent in the block-major host pool.  Eight CTAs: the link, not the GPU, is
-  // the limit (4 CTAs already fill PCIe outbound, 8 inbound).  A resident copy CTA takes its
-  // SM away from full-SM GEMM kernels that run at the same time, so larger grids only cost
-  // the forward pass the swap overlaps with, and they slow per-layer launches down.
-  constexpr int kSwapCtas = 8;
+  // which are adjacent in the block-major host pool.  Three CTAs of 1024 threads (64 KiB in
+  // flight each): the link, not the GPU, is the limit (2 such CTAs already fill PCIe
+  // outbound, 3 inbound; with 256-thread CTAs inbound needs 6), and a resident copy CTA takes
+  // its SM away from the full-SM GEMM kernels of the forward pass the swap overlaps with:
+  // measured against a stream of 8192^3 bf16 GEMMs, up to 3 copy CTAs cost them nothing,
+  // 4 cost 20 %, 5 or more 85 % and upwards.
+  constexpr int kSwapCtas = 3;
   if (direction == LMS_SWAP_OUT)
     return chunk_copy(g, gpu_layer_stride, gpu_block_stride, h,
                       host_layer_stride, host_block_stride, chunk_bytes, nl,
                       pairs, n_pairs, num_gpu_blocks, num_host_blocks,
                       /*layer_major=*/0, kWhereSwapOut,
-                      tuned_variant(LMS_TUNE_SWAP_VARIANT, 0), 0,
+                      tuned_variant(LMS_TUNE_SWAP_VARIANT, 4), 0,
                       tuned(LMS_TUNE_SWAP_OUT_CTAS, kSwapCtas), stream);
   return chunk_copy(h, host_layer_stride, host_block_stride, g,
                     gpu_layer_stride, gpu_block_stride, chunk_bytes, nl, pairs,
                     n_pairs, num_host_blocks, num_gpu_blocks,
                     /*layer_major=*/0, kWhereSwapIn,
-                    tuned_variant(LMS_TUNE_SWAP_VARIANT, 0), 0,
+                    tuned_variant(LMS_TUNE_SWAP_VARIANT, 4), 0,
                     tuned(LMS_TUNE_SWAP_IN_CTAS, kSwapCtas), stream);
 }
 

@@ -236,10 +236,8 @@ __global__ void __launch_bounds__(32) wait_selftest_kernel(ErrRecord* err,
     report(err, kErrWaitTimeout, kWhereSelfTest, 0, (long long)limit_ns);
 }
 
-template <class Vec, int POLICY>
+template <class Vec, int POLICY, int THREADS = 256, int VPT = 8>
 cudaError_t launch_vec(CopyParams p, int grid_ctas, cudaStream_t stream) {
-  constexpr int THREADS = 256;
-  constexpr int VPT = 8;
   constexpr int kSlice = THREADS * VPT * Vec::kBytes;  // bytes per CTA iteration
   p.slice_bytes = p.chunk_bytes < kSlice ? p.chunk_bytes : kSlice;
   p.slices = (p.chunk_bytes + p.slice_bytes - 1) / p.slice_bytes;
@@ -314,6 +312,9 @@ cudaError_t launch_chunk_copy(const CopyParams& p_in, int variant, int policy,
     chunk_copy_bulk<WARPS><<<(unsigned)ctas, WARPS * 32, smem, stream>>>(p);
     return cudaGetLastError();
   }
+  // Wide CTAs for grids of a few CTAs (the swap): 1024 threads keep 128 KiB in flight per CTA,
+  // which a read over PCIe needs to hide its latency without occupying more SMs.
+  if (variant == 4) return launch_vec<V16, 0, 1024, 8>(p, grid_ctas, stream);
   if (variant == 1)
     return policy == 1 ? launch_vec<V32, 1>(p, grid_ctas, stream)
                        : launch_vec<V32, 0>(p, grid_ctas, stream);

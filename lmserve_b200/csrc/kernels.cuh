@@ -1,6 +1,7 @@
 // Parameter blocks and host-side launchers of the data-movement kernels.
 // The C ABI (capi.cu) validates arguments, fills these structs and calls the
-// launchers; the kernels themselves live in write_rows.cu and chunk_copy.cu.
+// launchers; the kernels themselves live in write_rows.cu, chunk_copy.cu, rope_cache.cu and
+// step_indices.cu.
 #pragma once
 
 #include <cuda_runtime.h>
@@ -19,6 +20,7 @@ enum : unsigned int {
   kWhereTransfer = 5,
   kWhereRope = 6,
   kWhereSelfTest = 7,
+  kWhereStepIndices = 8,
 };
 
 // ------------------------------------------------------------ paged cache write
@@ -114,6 +116,32 @@ struct RopeParams {
 };
 
 cudaError_t launch_rope_cache(const RopeParams& p, bool pdl, cudaStream_t stream);
+
+// ------------------------------------------------------------ per-step index preparation
+struct StepIndexParams {
+  const int* input_len;    // [batch] new tokens of each request
+  const int* filled_len;   // [batch] tokens already in the cache
+  const int* context_len;  // [batch] tokens in the cache after this step
+  const int* num_blocks;   // [batch] entries of each request's block table
+  const int* block_ids;    // [total_blocks] the block tables, concatenated
+  const int* token_ids;    // [total_tokens], read only when input_ids is set
+  int batch;
+  int block_size;
+  long long total_tokens, total_blocks;
+  int* position_ids;        // [total_tokens]      every output may be nullptr
+  int* cu_seqlens_q;        // [batch + 1]
+  int* kv_block_indptrs;    // [batch + 1]
+  int* kv_block_indices;    // [total_blocks]
+  int* kv_last_block_lens;  // [batch]
+  int* batch_indices;       // [total_tokens]
+  int* positions;           // [total_tokens]
+  long long* slot_mapping;  // [total_tokens]
+  long long* input_ids;     // [total_tokens]
+  ErrRecord* err;
+  int checks;
+};
+
+cudaError_t launch_step_indices(const StepIndexParams& p, int sms, cudaStream_t stream);
 
 // One warp waits (bounded) on an mbarrier that is never completed; see lms_selftest_bounded_wait.
 cudaError_t launch_wait_selftest(ErrRecord* err, unsigned long long limit_ns, cudaStream_t stream);

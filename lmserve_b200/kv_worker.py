@@ -228,8 +228,8 @@ class KVWorker:
         cache_ops._require_cuda("gpu_kv_caches", gpu_kv_caches)
         if swap_engine not in ("kernel", "dma"):
             raise ValueError("swap_engine must be 'kernel' or 'dma'")
-        # "kernel": the sm_100a gather/scatter kernel on 16 CTAs - full PCIe rate even when
-        # launched once per layer, but a resident kernel costs concurrent full-SM GEMMs 10-90 %.
+        # "kernel": the sm_100a gather/scatter kernel on 3 CTAs - full PCIe rate even when
+        # launched once per layer, at a cost of about 10 % to concurrent full-SM GEMMs.
         # "dma": copy engines only, no SM is touched; full rate needs many layers per launch
         # (one 64 KiB copy per layer and block, the reference's pattern, reaches 13 GB/s).
         self.swap_engine = swap_engine

@@ -322,3 +322,38 @@ def config5_transfer(rank: int = 0, seed: int = 1005, num_blocks: Optional[int] 
     s = SHAPES["llama31_70b_tp8"]
     return make_transfer(s if num_blocks is None else s.scaled(num_blocks=num_blocks),
                          32, 2048, seed + 100 + rank)
+
+
+# ---------------------------------------------------------------- per-step request lists
+@dataclass
+class StepRequest:
+    """One scheduled request with the ``InferInput`` fields of ``proto/worker.proto:40-47``."""
+    input_ids: List[int]
+    input_len: int
+    filled_token_len: int
+    context_len: int
+    block_ids: List[int]
+    seq_id: int = 0
+
+
+def make_step_requests(num_blocks: int, block_size: int, num_decode: int, ctx_lo: int, ctx_hi: int,
+                       num_prefill: int, chunk_tokens: int, max_offset: int, seed: int,
+                       spare_blocks: int = 0, vocab: int = 128256) -> List[StepRequest]:
+    """A mixed step in scheduler order (seeded shuffle): `num_decode` requests with one new token
+    after ``ctx ~ U{ctx_lo..ctx_hi}`` cached tokens and `num_prefill` requests whose chunk of
+    `chunk_tokens` tokens starts at ``off ~ U{0..max_offset-1}``.  Block tables are dealt from a
+    seeded shuffle of the free list and hold exactly the blocks the context needs, plus
+    `spare_blocks` reserved ahead when asked for."""
+    rng = np.random.default_rng(seed)
+    filled = np.concatenate([rng.integers(ctx_lo, ctx_hi + 1, size=num_decode),
+                             rng.integers(0, max(max_offset, 1), size=num_prefill)]).astype(np.int64)
+    new = np.concatenate([np.ones(num_decode, np.int64), np.full(num_prefill, chunk_tokens, np.int64)])
+    ctx = filled + new
+    nblk = (ctx + block_size - 1) // block_size + spare_blocks
+    bt = deal_block_tables(rng, num_blocks, nblk)
+    reqs = [StepRequest(input_ids=rng.integers(0, vocab, size=int(q)).tolist(), input_len=int(q),
+                        filled_token_len=int(f), context_len=int(c),
+                        block_ids=[int(x) for x in t], seq_id=i)
+            for i, (q, f, c, t) in enumerate(zip(new, filled, ctx, bt.tables))]
+    order = rng.permutation(len(reqs))
+    return [reqs[i] for i in order]

@@ -47,7 +47,7 @@ def test_tuning_roundtrip_and_range():
     assert L.lms_set_tuning(_lib.TUNE_WRITE_VARIANT, -1) == 0
     assert L.lms_get_tuning(_lib.TUNE_WRITE_VARIANT) == -1
     assert L.lms_set_tuning(_lib.TUNE_WRITE_VARIANT, 5) == _lib.LMS_ERR_RANGE
-    assert L.lms_set_tuning(_lib.TUNE_COPY_VARIANT, 4) == _lib.LMS_ERR_RANGE
+    assert L.lms_set_tuning(_lib.TUNE_COPY_VARIANT, 5) == _lib.LMS_ERR_RANGE
     assert L.lms_set_tuning(0, 1) == _lib.LMS_ERR_RANGE
     assert L.lms_set_tuning(99, 1) == _lib.LMS_ERR_RANGE
     assert L.lms_set_tuning(_lib.TUNE_SWAP_OUT_CTAS, 64) == 0
