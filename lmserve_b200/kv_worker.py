@@ -102,6 +102,7 @@ class HostPool:
         self.device_ptr = dp.value
         self.array = flat.reshape(self.num_blocks, self.num_layers, self.chunk_bytes)
         self.tensor = torch.from_numpy(self.array)
+        cache_ops.HOST_POOL_DEVICE_PTR[self.host_ptr] = self.device_ptr
 
     @classmethod
     def from_buffer(cls, array: np.ndarray, num_layers: int, chunk_bytes: int) -> "HostPool":
@@ -119,6 +120,7 @@ class HostPool:
 
     def close(self) -> None:
         if getattr(self, "host_ptr", None):
+            cache_ops.HOST_POOL_DEVICE_PTR.pop(self.host_ptr, None)
             self.tensor = None
             self.array = None
             if self._registered is None:
