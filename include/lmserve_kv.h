@@ -257,15 +257,21 @@ int lms_build_step_indices(const int32_t* input_len, const int32_t* filled_len,
  * bytes), positions int32 (positions_are_int64 = 0) or int64 [T], cos_sin_cache
  * [max_position, 2*head_dim] = the cos row then the sin row of a position (row stride in
  * bytes).  For every head, x = first half, y = second half:
- *   out_x = x*cos[i] - y*sin[i],  out_y = y*cos[D/2+i] + x*sin[D/2+i],
- * every product and sum rounded to the element type (dtype 0 = fp16, 1 = bf16), which is the
- * arithmetic of the Triton kernel evaluated one operation at a time.  Rotated Q goes to q_out;
+ *   out_x = x*cos[i] - y*sin[i],  out_y = y*cos[D/2+i] + x*sin[D/2+i]
+ * in the element type (dtype 0 = fp16, 1 = bf16).  `arithmetic` selects how the two lines are
+ * rounded: LMS_ROPE_CONTRACTED = as the Triton compiler emits them for a GPU, the first product
+ * of each line fused into the sum, out_x = fma(x, cos[i], -rn(y*sin[i])), out_y =
+ * fma(y, cos[D/2+i], rn(x*sin[D/2+i])) — the results the reference produces when it runs;
+ * LMS_ROPE_ROUND_EACH = every product and sum rounded on its own, the Triton language
+ * semantics and the result of the Triton interpreter.  Rotated Q goes to q_out;
  * rotated K goes to k_out if it is not NULL and, if the caches are not NULL, to the key-cache
  * row of slot_mapping[t]; V is copied to the value-cache row.  Cache addressing, the slot < 0
  * padding rule and num_slots are those of lms_reshape_and_cache.  Only the full rotary
  * dimension (rotary_dim == head_dim, a multiple of 16) is supported, which covers the Llama
  * and Qwen2 models of the reference.  max_position: debug checks only (0 = unknown).
  */
+#define LMS_ROPE_CONTRACTED 0
+#define LMS_ROPE_ROUND_EACH 1
 int lms_rope_and_cache(const void* query, const void* key, const void* value,
                        int64_t query_token_stride, int64_t key_token_stride,
                        int64_t value_token_stride, const void* positions,
@@ -276,8 +282,8 @@ int lms_rope_and_cache(const void* query, const void* key, const void* value,
                        void* value_cache, int64_t block_stride, int64_t slot_stride,
                        const int64_t* slot_mapping, int64_t num_tokens,
                        int32_t num_heads, int32_t num_kv_heads, int32_t head_dim,
-                       int32_t dtype, int32_t block_size, int64_t num_slots,
-                       int64_t max_position, void* stream);
+                       int32_t dtype, int32_t arithmetic, int32_t block_size,
+                       int64_t num_slots, int64_t max_position, void* stream);
 
 /*
  * Copy-on-write block copy — replaces

@@ -21,6 +21,8 @@ LMS_ERR_PEER = -6
 LMS_ERR_UNSUPPORTED = -7
 LMS_ERR_TOO_LARGE = -8
 LMS_STATIC_MAX_PAIRS = 16384
+LMS_ROPE_CONTRACTED = 0
+LMS_ROPE_ROUND_EACH = 1
 
 LMS_SWAP_OUT = 0
 LMS_SWAP_IN = 1
@@ -68,7 +70,7 @@ SIGNATURES = {
     "lms_rope_and_cache": (c_int, [
         c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int32, c_void_p,
         c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int64,
-        c_void_p, c_int64, c_int32, c_int32, c_int32, c_int32, c_int32, c_int64, c_int64,
+        c_void_p, c_int64, c_int32, c_int32, c_int32, c_int32, c_int32, c_int32, c_int64, c_int64,
         c_void_p]),
     "lms_build_step_indices": (c_int, [
         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int64, c_int64,

@@ -522,10 +522,11 @@ int lms_rope_and_cache(const void* query, const void* key, const void* value,
                        void* value_cache, int64_t block_stride, int64_t slot_stride,
                        const int64_t* slot_mapping, int64_t num_tokens,
                        int32_t num_heads, int32_t num_kv_heads, int32_t head_dim,
-                       int32_t dtype, int32_t block_size, int64_t num_slots,
-                       int64_t max_position, void* stream) {
+                       int32_t dtype, int32_t arithmetic, int32_t block_size,
+                       int64_t num_slots, int64_t max_position, void* stream) {
   if (num_tokens < 0 || num_tokens > 0x7fffffffll || num_heads <= 0 || num_kv_heads <= 0 ||
-      head_dim <= 0 || num_slots < 0 || max_position < 0 || (dtype != 0 && dtype != 1))
+      head_dim <= 0 || num_slots < 0 || max_position < 0 || (dtype != 0 && dtype != 1) ||
+      (arithmetic != LMS_ROPE_CONTRACTED && arithmetic != LMS_ROPE_ROUND_EACH))
     return LMS_ERR_RANGE;
   if (head_dim % 16 != 0) return LMS_ERR_UNSUPPORTED;
   if (num_tokens == 0) return LMS_OK;
@@ -574,6 +575,7 @@ int lms_rope_and_cache(const void* query, const void* key, const void* value,
   p.head_dim = head_dim;
   p.block_size = cached ? block_size : 1;
   p.is_bf16 = dtype;
+  p.fused = arithmetic == LMS_ROPE_CONTRACTED ? 1 : 0;
   p.err = ds->err.load(std::memory_order_relaxed);
   p.checks = g_checks.load(std::memory_order_relaxed);
   LMS_CUDA(launch_rope_cache(p, tuned(LMS_TUNE_WRITE_PDL, 1) == 1, (cudaStream_t)stream));

@@ -111,6 +111,7 @@ struct RopeParams {
   int num_tokens, num_heads, num_kv_heads, head_dim;
   int block_size, block_shift;
   int is_bf16;
+  int fused;  // 1: contracted as the Triton compiler emits it, 0: every operation rounded
   ErrRecord* err;
   int checks;
 };

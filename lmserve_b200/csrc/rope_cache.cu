@@ -7,13 +7,21 @@
 // (and into a K output buffer if the caller wants one), and copies V into the cache.
 //
 // Arithmetic follows LMServe's Triton kernel (ops/triton/rotary_embedding.py:5-66), element
-// type in, element type out, every product and every sum rounded to the element type:
+// type in, element type out:
 //   x = head[0 : D/2], y = head[D/2 : D]          (rotate-half pairing)
 //   out_x = x * cos[i]       - y * sin[i]
 //   out_y = y * cos[D/2 + i] + x * sin[D/2 + i]
-// with cos = cos_sin_cache[pos, 0:D], sin = cos_sin_cache[pos, D:2D].  The *_rn intrinsics
-// keep the compiler from contracting a product and a sum into one fused operation, so the
-// result is bit-identical to evaluating the expression one rounded operation at a time.
+// with cos = cos_sin_cache[pos, 0:D], sin = cos_sin_cache[pos, D:2D].  Two evaluations of that
+// expression exist and both are offered:
+//   * contracted (FUSED): what the Triton compiler emits for a GPU - the first product of each
+//     line is fused into the sum, the second product is rounded on its own:
+//       out_x = fma(x, cos[i], -rn(y * sin[i])),  out_y = fma(y, cos[D/2+i], rn(x * sin[D/2+i]))
+//     (measured on B200 against a compiled Triton kernel of the same two lines: identical);
+//   * every product and every sum rounded to the element type, which is the Triton language
+//     semantics and what the Triton interpreter computes.  The *_rn intrinsics keep the
+//     compiler from contracting, so the result is bit-identical to one rounded operation at a
+//     time.
+// The two differ by one unit in the last place in about a quarter of the elements.
 //
 // One thread owns 8 consecutive x elements and the 8 matching y elements of one head of one
 // token (two 16-byte loads from the head, four from the cos/sin row, two 16-byte stores).
@@ -46,7 +54,12 @@ __device__ __forceinline__ __nv_bfloat162 mul_rn(__nv_bfloat162 a, __nv_bfloat16
 __device__ __forceinline__ __nv_bfloat162 add_rn(__nv_bfloat162 a, __nv_bfloat162 b) { return __hadd2_rn(a, b); }
 __device__ __forceinline__ __nv_bfloat162 sub_rn(__nv_bfloat162 a, __nv_bfloat162 b) { return __hsub2_rn(a, b); }
 
-template <class T2, int THREADS>
+__device__ __forceinline__ __half2 fma_rn(__half2 a, __half2 b, __half2 c) { return __hfma2(a, b, c); }
+__device__ __forceinline__ __nv_bfloat162 fma_rn(__nv_bfloat162 a, __nv_bfloat162 b, __nv_bfloat162 c) { return __hfma2(a, b, c); }
+__device__ __forceinline__ __half2 neg(__half2 a) { return __hneg2(a); }
+__device__ __forceinline__ __nv_bfloat162 neg(__nv_bfloat162 a) { return __hneg2(a); }
+
+template <class T2, int THREADS, bool FUSED>
 __global__ void __launch_bounds__(THREADS)
 rope_cache_kernel(const RopeParams p, const int items_per_head, const int heads_total,
                   const long long n_items) {
@@ -123,8 +136,13 @@ rope_cache_kernel(const RopeParams p, const int items_per_head, const int heads_
   Pack8<T2> ox, oy;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    ox.v[i] = sub_rn(mul_rn(x.v[i], cx.v[i]), mul_rn(y.v[i], sx.v[i]));
-    oy.v[i] = add_rn(mul_rn(y.v[i], cy.v[i]), mul_rn(x.v[i], sy.v[i]));
+    if (FUSED) {
+      ox.v[i] = fma_rn(x.v[i], cx.v[i], neg(mul_rn(y.v[i], sx.v[i])));
+      oy.v[i] = fma_rn(y.v[i], cy.v[i], mul_rn(x.v[i], sy.v[i]));
+    } else {
+      ox.v[i] = sub_rn(mul_rn(x.v[i], cx.v[i]), mul_rn(y.v[i], sx.v[i]));
+      oy.v[i] = add_rn(mul_rn(y.v[i], cy.v[i]), mul_rn(x.v[i], sy.v[i]));
+    }
   }
 
   if (is_q) {
@@ -173,10 +191,14 @@ cudaError_t launch_rope_cache(const RopeParams& p_in, bool pdl, cudaStream_t str
     cfg.numAttrs = 1;
   }
   if (p.is_bf16)
-    return cudaLaunchKernelEx(&cfg, rope_cache_kernel<__nv_bfloat162, THREADS>, p,
-                              items_per_head, heads_total, n_items);
-  return cudaLaunchKernelEx(&cfg, rope_cache_kernel<__half2, THREADS>, p, items_per_head,
-                            heads_total, n_items);
+    return p.fused ? cudaLaunchKernelEx(&cfg, rope_cache_kernel<__nv_bfloat162, THREADS, true>, p,
+                                        items_per_head, heads_total, n_items)
+                   : cudaLaunchKernelEx(&cfg, rope_cache_kernel<__nv_bfloat162, THREADS, false>, p,
+                                        items_per_head, heads_total, n_items);
+  return p.fused ? cudaLaunchKernelEx(&cfg, rope_cache_kernel<__half2, THREADS, true>, p,
+                                      items_per_head, heads_total, n_items)
+                 : cudaLaunchKernelEx(&cfg, rope_cache_kernel<__half2, THREADS, false>, p,
+                                      items_per_head, heads_total, n_items);
 }
 
 }  // namespace lms

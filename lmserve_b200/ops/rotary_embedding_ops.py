@@ -66,7 +66,13 @@ def _check_inputs(query, key, positions, cos_sin_cache, head_dim):
         raise TypeError("positions must be int32 or int64 with one entry per token")
 
 
-def _launch(query, key, value, positions, cos_sin_cache, head_dim, q_out, k_out, kv_cache, slots):
+_ARITHMETIC = {"compiled": _lib.LMS_ROPE_CONTRACTED, "round_each": _lib.LMS_ROPE_ROUND_EACH}
+
+
+def _launch(query, key, value, positions, cos_sin_cache, head_dim, q_out, k_out, kv_cache, slots,
+            arithmetic="compiled"):
+    if arithmetic not in _ARITHMETIC:
+        raise ValueError(f"arithmetic must be 'compiled' or 'round_each', got {arithmetic!r}")
     dev = query.device
     es = query.element_size()
     T = query.shape[0]
@@ -90,30 +96,40 @@ def _launch(query, key, value, positions, cos_sin_cache, head_dim, q_out, k_out,
             k_out.data_ptr() if k_out is not None else None,
             k_out.stride(0) * es if k_out is not None else 0,
             kptr, vptr, block_stride, slot_stride, sp, T, nh, nkv, head_dim,
-            _DTYPE_CODE[query.dtype], BS, ns, cos_sin_cache.shape[0], _stream_ptr(dev)))
+            _DTYPE_CODE[query.dtype], _ARITHMETIC[arithmetic], BS, ns, cos_sin_cache.shape[0],
+            _stream_ptr(dev)))
 
 
 def rotary_pos_emb(query: torch.Tensor, key: torch.Tensor, positions: torch.Tensor,
-                   cos_sin_cache: torch.Tensor, head_dim: int) -> Tuple[torch.Tensor, torch.Tensor]:
+                   cos_sin_cache: torch.Tensor, head_dim: int,
+                   arithmetic: str = "compiled") -> Tuple[torch.Tensor, torch.Tensor]:
     """``(q_out, k_out)``: query ``[T, num_heads*head_dim]`` and key ``[T, num_kv_heads*head_dim]``
-    rotated by ``cos_sin_cache[positions]`` — LMServe's ``rotary_pos_emb``."""
+    rotated by ``cos_sin_cache[positions]`` — LMServe's ``rotary_pos_emb``.
+
+    ``arithmetic="compiled"`` (default) rounds as the Triton compiler's GPU code for the
+    reference kernel does (the first product of ``x*cos - y*sin`` and of ``y*cos + x*sin`` fused
+    into the sum), i.e. it returns what the reference returns when it runs on a GPU;
+    ``"round_each"`` rounds every product and sum, the Triton language semantics (and the result
+    of the Triton interpreter).  The two differ by one unit in the last place in about a quarter
+    of the elements."""
     _check_inputs(query, key, positions, cos_sin_cache, head_dim)
     q_out = torch.empty_like(query, memory_format=torch.contiguous_format)
     k_out = torch.empty_like(key, memory_format=torch.contiguous_format)
     if query.shape[0]:
-        _launch(query, key, None, positions, cos_sin_cache, head_dim, q_out, k_out, None, None)
+        _launch(query, key, None, positions, cos_sin_cache, head_dim, q_out, k_out, None, None,
+                arithmetic)
     return q_out, k_out
 
 
 def rotary_pos_emb_and_cache(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
                              positions: torch.Tensor, cos_sin_cache: torch.Tensor, head_dim: int,
                              kv_cache: torch.Tensor, slot_mapping: torch.Tensor,
-                             return_key: bool = False):
+                             return_key: bool = False, arithmetic: str = "compiled"):
     """Rotates ``query`` (returned) and ``key``, and writes rotated K and ``value`` into
     ``kv_cache`` (one layer, ``[num_blocks, 2, block_size, H, D]``) at ``slot_mapping`` in the same
     launch.  ``slot_mapping[t] < 0`` skips the cache write of token ``t``.  With
     ``return_key=True`` the rotated key is returned as well (``(q_out, k_out)``), for callers
-    that still need it outside the cache."""
+    that still need it outside the cache.  ``arithmetic`` as in :func:`rotary_pos_emb`."""
     _check_inputs(query, key, positions, cos_sin_cache, head_dim)
     _require_cuda("value", value)
     _require_cuda("kv_cache", kv_cache)
@@ -132,5 +148,6 @@ def rotary_pos_emb_and_cache(query: torch.Tensor, key: torch.Tensor, value: torc
     q_out = torch.empty_like(query, memory_format=torch.contiguous_format)
     k_out = torch.empty_like(key, memory_format=torch.contiguous_format) if return_key else None
     if query.shape[0]:
-        _launch(query, key, value, positions, cos_sin_cache, head_dim, q_out, k_out, kv_cache, slots)
+        _launch(query, key, value, positions, cos_sin_cache, head_dim, q_out, k_out, kv_cache, slots,
+                arithmetic)
     return (q_out, k_out) if return_key else q_out

@@ -12,6 +12,9 @@ the Triton interpreter; the outputs are committed under ``tests/golden/`` togeth
 with ``tests/golden/make_golden.py`` that produced them.  The swap and transfer
 restatements have no executable reference (pycuda / NIXL are not installable
 here) and follow ``kv_worker.py`` by reading: for those two, parity is unpinned.
+``rope_oracle`` has two arithmetic forms: rounded per operation (pinned for fp16 by the
+reference kernel under the Triton interpreter) and contracted as compiled Triton evaluates it
+(pinned for fp16 and bf16 by vectors made on a B200, ``tests/golden/rope_compiled_*.npz``).
 ``step_oracle`` (per-step index preparation) restates ``model_worker.py:310-433`` and the two
 flashinfer helpers it calls; it is pinned by the worked example in flashinfer's documentation
 and, on a GPU box, by the installed flashinfer functions themselves.

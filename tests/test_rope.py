@@ -37,6 +37,31 @@ def test_oracle_matches_reference_kernel_fp16(name):
     assert torch.allclose(once.view_as(q), qo.float(), atol=4e-3, rtol=4e-3)
 
 
+COMPILED_CASES = [("rope_compiled_fp16", "fp16"), ("rope_compiled_bf16", "bf16")]
+
+
+def compiled_golden(name, dt):
+    z = np.load(str(__import__("helpers").GOLDEN / f"{name}.npz"))
+    f = lambda k: to_tensor(z[k], dt)
+    return (int(z["head_dim"]), f("query"), f("key"), torch.from_numpy(z["positions"]),
+            f("cos_sin_cache"), z["q_out"], z["k_out"])
+
+
+@pytest.mark.parametrize("name,dt", COMPILED_CASES)
+def test_contracted_oracle_matches_compiled_triton_kernel(name, dt):
+    """The golden vectors come from a compiled Triton kernel on a B200: the first product of
+    each line is fused into the sum.  fp16 and bf16."""
+    hd, q, k, pos, cs, q_out, k_out = compiled_golden(name, dt)
+    qo, ko = rope_oracle.rotary_pos_emb(q, k, pos, cs, hd, contracted=True)
+    assert np.array_equal(to_words(qo), q_out)
+    assert np.array_equal(to_words(ko), k_out)
+    # and the distinction matters: rounding every operation gives other last bits
+    qe, _ = rope_oracle.rotary_pos_emb(q, k, pos, cs, hd, contracted=False)
+    differ = (to_words(qe) != q_out).mean()
+    assert 0.05 < differ < 0.5
+    assert torch.allclose(qe.float(), qo.float(), atol=2e-2, rtol=2e-2)
+
+
 def test_package_cos_sin_cache_matches_oracle_and_llama3_scaling():
     from lmserve_b200.ops import build_cos_sin_cache
     a = build_cos_sin_cache(128, 64, torch.bfloat16, base=500000.0)
@@ -71,11 +96,25 @@ def test_rotary_pos_emb_golden_gpu(name):
     from lmserve_b200.ops import rotary_pos_emb
     hd, q, k, pos, cs, q_out, k_out = golden(name)
     before = _lib.lib().lms_launch_count()
-    qo, ko = rotary_pos_emb(q.to(DEV), k.to(DEV), pos.to(DEV), cs.to(DEV), hd)
+    qo, ko = rotary_pos_emb(q.to(DEV), k.to(DEV), pos.to(DEV), cs.to(DEV), hd, arithmetic="round_each")
     torch.cuda.synchronize()
     assert _lib.lib().lms_launch_count() == before + 1
     assert np.array_equal(to_words(qo), q_out)
     assert np.array_equal(to_words(ko), k_out)
+
+
+@gpu
+@pytest.mark.parametrize("name,dt", COMPILED_CASES)
+def test_rotary_pos_emb_compiled_golden_gpu(name, dt):
+    """Default arithmetic = what the compiled reference kernel returns on a GPU."""
+    from lmserve_b200.ops import rotary_pos_emb
+    hd, q, k, pos, cs, q_out, k_out = compiled_golden(name, dt)
+    qo, ko = rotary_pos_emb(q.to(DEV), k.to(DEV), pos.to(DEV), cs.to(DEV), hd)
+    torch.cuda.synchronize()
+    assert np.array_equal(to_words(qo), q_out)
+    assert np.array_equal(to_words(ko), k_out)
+    with pytest.raises(ValueError, match="arithmetic"):
+        rotary_pos_emb(q.to(DEV), k.to(DEV), pos.to(DEV), cs.to(DEV), hd, arithmetic="fp32")
 
 
 def fused_case(dtype, seed, T=37, NH=8, NKV=2, HD=128, NB=24, BS=16, max_pos=300, pos_dtype=torch.int32):
@@ -93,10 +132,11 @@ def fused_case(dtype, seed, T=37, NH=8, NKV=2, HD=128, NB=24, BS=16, max_pos=300
 @gpu
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("pos_dtype", [torch.int32, torch.int64])
-def test_rotary_and_cache_fused_vs_oracle(dtype, pos_dtype):
+@pytest.mark.parametrize("arithmetic", ["compiled", "round_each"])
+def test_rotary_and_cache_fused_vs_oracle(dtype, pos_dtype, arithmetic):
     from lmserve_b200.ops import rotary_pos_emb, rotary_pos_emb_and_cache
     q, k, v, pos, cs, cache, slots, hd = fused_case(dtype, 7, pos_dtype=pos_dtype)
-    want_q, want_k = rope_oracle.rotary_pos_emb(q, k, pos, cs, hd)
+    want_q, want_k = rope_oracle.rotary_pos_emb(q, k, pos, cs, hd, contracted=arithmetic == "compiled")
     want_cache = to_words(cache).copy()
     T = q.shape[0]
     cache_oracle.reshape_and_cache(to_words(want_k).reshape(T, -1, hd), to_words(v).reshape(T, -1, hd),
@@ -104,21 +144,23 @@ def test_rotary_and_cache_fused_vs_oracle(dtype, pos_dtype):
     d = lambda t: t.to(DEV)
     got_cache = d(cache)
     qo, ko = rotary_pos_emb_and_cache(d(q), d(k), d(v), d(pos), d(cs), hd, got_cache, d(slots),
-                                      return_key=True)
+                                      return_key=True, arithmetic=arithmetic)
     torch.cuda.synchronize()
     assert np.array_equal(to_words(qo), to_words(want_q))
     assert np.array_equal(to_words(ko), to_words(want_k))
     assert np.array_equal(to_words(got_cache), want_cache)
     # without the key output, and the unfused op, give the same tensors
     cache2 = d(cache)
-    qo2 = rotary_pos_emb_and_cache(d(q), d(k), d(v), d(pos), d(cs), hd, cache2, d(slots))
-    qo3, ko3 = rotary_pos_emb(d(q), d(k), d(pos), d(cs), hd)
+    qo2 = rotary_pos_emb_and_cache(d(q), d(k), d(v), d(pos), d(cs), hd, cache2, d(slots), arithmetic=arithmetic)
+    qo3, ko3 = rotary_pos_emb(d(q), d(k), d(pos), d(cs), hd, arithmetic=arithmetic)
     torch.cuda.synchronize()
     assert torch.equal(qo2.view(torch.int16), qo.view(torch.int16))
     assert torch.equal(cache2.view(torch.int16), got_cache.view(torch.int16))
     assert torch.equal(qo3.view(torch.int16), qo.view(torch.int16))
     assert torch.equal(ko3.view(torch.int16), ko.view(torch.int16))
-    # the same values on the device one torch operation at a time (the Triton kernel's semantics)
+    if arithmetic != "round_each":
+        return
+    # the same values on the device one torch operation at a time (the Triton language semantics)
     E = hd // 2
     h = d(q).view(T, -1, hd)
     row = d(cs)[d(pos).long()]
@@ -166,7 +208,7 @@ def test_rotary_and_cache_llama_decode_shape_bf16():
     from lmserve_b200.ops import rotary_pos_emb_and_cache
     q, k, v, pos, cs, cache, slots, hd = fused_case(torch.bfloat16, 11, T=256, NH=32, NKV=8, HD=128,
                                                      NB=64, max_pos=4096)
-    want_q, want_k = rope_oracle.rotary_pos_emb(q, k, pos, cs, hd)
+    want_q, want_k = rope_oracle.rotary_pos_emb(q, k, pos, cs, hd, contracted=True)
     want_cache = to_words(cache).copy()
     cache_oracle.reshape_and_cache(to_words(want_k).reshape(256, -1, hd), to_words(v).reshape(256, -1, hd),
                                    want_cache, slots.numpy())
