@@ -555,6 +555,40 @@ def bench_swap(comm, stream, cache_view, dev, args, sampler):
             b = torch.randn(8192, 8192, device=dev, dtype=torch.bfloat16)
             copy_stream = torch.cuda.Stream()
 
+            # the layer handshake end to end: a stand-in forward pass (3 GEMMs per layer) whose
+            # layer l waits for pre_events[l], against a swap-in issued layer by layer on the
+            # worker's stream (kv_worker.py:249-270 / model_worker.py:232-276 in LMServe)
+            quarter = w.in_pairs[: max(1, n_blocks // 4)]
+            worker.swap_engine = "kernel"
+
+            def forward(events):
+                for l in range(s.num_layers):
+                    if events is not None:
+                        stream.wait_event(events[l])
+                    for _ in range(3):
+                        torch.matmul(a, b)
+
+            def pipelined(i):
+                copy_stream.wait_stream(stream)
+                worker._swap([quarter], "in", copy_stream, pre, None, 1)
+                forward(pre)
+
+            def serial(i):
+                worker._swap([quarter], "in", stream, pre, None, 1)
+                forward(None)
+
+            forward(None)
+            ms_f = timed(comm, stream, lambda i: forward(None), 1, 1, sampler)
+            ms_s = timed(comm, stream, lambda i: worker._swap([quarter], "in", stream, pre, None, 1), 1, 1, sampler)
+            ms_ser = timed(comm, stream, serial, 1, 1, sampler)
+            ms_p = timed(comm, stream, pipelined, 1, 1, sampler)
+            out["swap_in_pipelined_with_forward"] = {
+                "forward_alone_ms": ms_f, "swap_in_alone_ms": ms_s, "one_after_the_other_ms": ms_ser,
+                "layer_pipelined_ms": ms_p, "lower_bound_ms": max(ms_f, ms_s),
+                "hidden_fraction_of_the_shorter": (ms_f + ms_s - ms_p) / min(ms_f, ms_s),
+                "note": f"{len(quarter)} blocks x {s.num_layers} layers x 64 KiB swapped in, one launch and "
+                        "one event per layer; forward = 3 bf16 GEMMs of 8192^3 per layer gated on that event"}
+
             def gemms(engine):
                 """150 GEMMs on the main thread and stream; the swap is issued at the same
                 moment from a second host thread on its own stream (as a KV worker would)."""
