@@ -4,8 +4,11 @@ nvcc compiles the ``csrc/*.cu`` files for sm_100a only; the result links the
 static CUDA runtime and nothing else, so it can be loaded with ``ctypes`` (or
 bound from cgo / JNI / FFI) without PyTorch.
 
-Run ``python -m lmserve_b200.build`` to (re)build; ``build_library()`` is what
-``__graft_entry__.build()`` calls.
+``build_packer()`` compiles the small CPython extension ``_packer`` (``csrc/packer.c``, gcc)
+that packs a step's request list for ``lms_build_step_indices``; it is host code only.
+
+Run ``python -m lmserve_b200.build`` to (re)build both; ``build_library()`` and
+``build_packer()`` are what ``__graft_entry__.build()`` calls.
 """
 from __future__ import annotations
 
@@ -75,6 +78,30 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
     return LIB_PATH
 
 
+PACKER_SRC = CSRC / "packer.c"
+PACKER_PATH = PKG_DIR / "_packer.so"
+
+
+def build_packer(force: bool = False) -> Path:
+    """Compiles ``lmserve_b200/_packer.so`` (CPython C API, no CUDA) if it is missing or stale."""
+    import sysconfig
+    if (not force and PACKER_PATH.exists()
+            and PACKER_PATH.stat().st_mtime >= max(PACKER_SRC.stat().st_mtime, Path(__file__).stat().st_mtime)):
+        return PACKER_PATH
+    cc = os.environ.get("CC") or shutil.which("gcc") or shutil.which("cc")
+    if not cc:
+        raise RuntimeError("no C compiler found for the request packer; set CC")
+    tmp = PACKER_PATH.with_suffix(".so.tmp")
+    cmd = [cc, "-O2", "-fPIC", "-shared", "-Wall", "-I", sysconfig.get_paths()["include"],
+           str(PACKER_SRC), "-o", str(tmp)]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"compiling the request packer failed:\n{res.stdout}\n{res.stderr}")
+    os.replace(tmp, PACKER_PATH)
+    return PACKER_PATH
+
+
 if __name__ == "__main__":
     path = build_library(force="--force" in sys.argv, verbose="-v" in sys.argv)
     print(path)
+    print(build_packer(force="--force" in sys.argv))

@@ -1,0 +1,161 @@
+/* Host-side packing of one step's request list into the int32 upload buffer of
+ * lms_build_step_indices, as a CPython extension module (lmserve_b200._packer).
+ *
+ * LMServe's model worker walks the request list in Python and builds one list per index array
+ * (runtime/worker/llm_worker/model_worker.py:330-407); converting those lists element by element
+ * is what its per-step preparation costs.  This module walks the same request objects in C and
+ * writes
+ *     [input_len | filled_token_len | context_len | len(block_ids)]   (batch entries each)
+ *     block_ids of every request, concatenated
+ *     input_ids of every request, concatenated
+ * straight into a caller-provided buffer (the pinned staging memory).  The requests are any
+ * objects with the InferInput attributes of proto/worker.proto:40-47; block_ids and input_ids are
+ * any sequences of integers.  Sorting stays with the caller (list.sort, as the reference does).
+ */
+#define PY_SSIZE_T_CLEAN
+#include <Python.h>
+#include <stdint.h>
+
+static int get_i32(PyObject* obj, const char* name, int32_t* out) {
+  PyObject* v = PyObject_GetAttrString(obj, name);
+  if (!v) return -1;
+  long long x = PyLong_AsLongLong(v);
+  Py_DECREF(v);
+  if (x == -1 && PyErr_Occurred()) return -1;
+  if (x < INT32_MIN || x > INT32_MAX) {
+    PyErr_Format(PyExc_OverflowError, "%s does not fit 32 bits", name);
+    return -1;
+  }
+  *out = (int32_t)x;
+  return 0;
+}
+
+/* Copies the integers of `seq` (already a list or tuple) to dst[0..n). */
+static int copy_ints(PyObject* fast, Py_ssize_t n, int32_t* dst, const char* what) {
+  PyObject** items = PySequence_Fast_ITEMS(fast);
+  for (Py_ssize_t i = 0; i < n; ++i) {
+    long long x = PyLong_AsLongLong(items[i]);
+    if (x == -1 && PyErr_Occurred()) return -1;
+    if (x < INT32_MIN || x > INT32_MAX) {
+      PyErr_Format(PyExc_OverflowError, "%s entry does not fit 32 bits", what);
+      return -1;
+    }
+    dst[i] = (int32_t)x;
+  }
+  return 0;
+}
+
+/* pack(inputs, out) -> (batch, total_tokens, total_blocks, prefill_input_len, num_prefill, num_decode)
+ * `out` is a writable, C-contiguous buffer of int32 (a numpy array); ValueError when it is too
+ * small or when a request is inconsistent, with the messages of the pure-Python packer. */
+static PyObject* pack(PyObject* self, PyObject* args) {
+  PyObject* inputs;
+  Py_buffer out;
+  if (!PyArg_ParseTuple(args, "Ow*", &inputs, &out)) return NULL;
+  PyObject* result = NULL;
+  PyObject* reqs = PySequence_Fast(inputs, "inputs must be a sequence of requests");
+  PyObject** blocks = NULL;
+  PyObject** ids = NULL;
+  Py_ssize_t batch = 0;
+  if (!reqs) goto done;
+  if (out.itemsize != 4 && out.itemsize != 1) {
+    PyErr_SetString(PyExc_TypeError, "out must be an int32 (or byte) buffer");
+    goto done;
+  }
+  batch = PySequence_Fast_GET_SIZE(reqs);
+  {
+    const Py_ssize_t cap = out.len / 4;
+    int32_t* buf = (int32_t*)out.buf;
+    if (4 * batch > cap) {
+      PyErr_Format(PyExc_ValueError, "step needs at least %zd int32 words of staging, the buffer has %zd",
+                   4 * batch, cap);
+      goto done;
+    }
+    blocks = (PyObject**)PyMem_Calloc(batch ? batch : 1, sizeof(PyObject*));
+    ids = (PyObject**)PyMem_Calloc(batch ? batch : 1, sizeof(PyObject*));
+    if (!blocks || !ids) {
+      PyErr_NoMemory();
+      goto done;
+    }
+    long long total_tokens = 0, total_blocks = 0, prefill_len = 0, n_pre = 0, n_dec = 0;
+    for (Py_ssize_t b = 0; b < batch; ++b) {
+      PyObject* r = PySequence_Fast_GET_ITEM(reqs, b);
+      int32_t q, filled, ctx;
+      if (get_i32(r, "input_len", &q) || get_i32(r, "filled_token_len", &filled) ||
+          get_i32(r, "context_len", &ctx))
+        goto done;
+      PyObject* a = PyObject_GetAttrString(r, "block_ids");
+      if (!a) goto done;
+      blocks[b] = PySequence_Fast(a, "block_ids must be a sequence");
+      Py_DECREF(a);
+      if (!blocks[b]) goto done;
+      a = PyObject_GetAttrString(r, "input_ids");
+      if (!a) goto done;
+      ids[b] = PySequence_Fast(a, "input_ids must be a sequence");
+      Py_DECREF(a);
+      if (!ids[b]) goto done;
+      const Py_ssize_t n_ids = PySequence_Fast_GET_SIZE(ids[b]);
+      if (n_ids != q) {
+        PyErr_Format(PyExc_ValueError, "request %zd: input_len %d but %zd input ids", b, (int)q, n_ids);
+        goto done;
+      }
+      if ((long long)ctx - filled != q) {
+        PyErr_Format(PyExc_ValueError,
+                     "request %zd: context_len - filled_token_len = %lld but input_len = %d", b,
+                     (long long)ctx - filled, (int)q);
+        goto done;
+      }
+      if (q > 1) {
+        prefill_len += q;
+        ++n_pre;
+      } else if (q == 1) {
+        ++n_dec;
+      }
+      const Py_ssize_t nb = PySequence_Fast_GET_SIZE(blocks[b]);
+      buf[b] = q;
+      buf[batch + b] = filled;
+      buf[2 * batch + b] = ctx;
+      buf[3 * batch + b] = (int32_t)nb;
+      total_tokens += q > 0 ? q : 0;
+      total_blocks += nb;
+    }
+    const long long need = 4 * (long long)batch + total_blocks + total_tokens;
+    if (need > cap || total_blocks > INT32_MAX || total_tokens > INT32_MAX) {
+      PyErr_Format(PyExc_ValueError, "step needs %lld int32 words of staging, the buffer has %zd", need, cap);
+      goto done;
+    }
+    int32_t* dst = buf + 4 * batch;
+    for (Py_ssize_t b = 0; b < batch; ++b) {
+      const Py_ssize_t nb = PySequence_Fast_GET_SIZE(blocks[b]);
+      if (copy_ints(blocks[b], nb, dst, "block_ids")) goto done;
+      dst += nb;
+    }
+    for (Py_ssize_t b = 0; b < batch; ++b) {
+      const Py_ssize_t n = PySequence_Fast_GET_SIZE(ids[b]);
+      if (copy_ints(ids[b], n, dst, "input_ids")) goto done;
+      dst += n;
+    }
+    result = Py_BuildValue("(nLLLLL)", batch, total_tokens, total_blocks, prefill_len, n_pre, n_dec);
+  }
+done:
+  if (blocks)
+    for (Py_ssize_t b = 0; b < batch; ++b) Py_XDECREF(blocks[b]);
+  if (ids)
+    for (Py_ssize_t b = 0; b < batch; ++b) Py_XDECREF(ids[b]);
+  PyMem_Free(blocks);
+  PyMem_Free(ids);
+  Py_XDECREF(reqs);
+  PyBuffer_Release(&out);
+  return result;
+}
+
+static PyMethodDef methods[] = {
+    {"pack", pack, METH_VARARGS,
+     "pack(inputs, out) -> (batch, total_tokens, total_blocks, prefill_input_len, num_prefill, num_decode)"},
+    {NULL, NULL, 0, NULL}};
+
+static struct PyModuleDef module = {PyModuleDef_HEAD_INIT, "_packer",
+                                    "Packs a step's request list into the index-preparation upload buffer.",
+                                    -1, methods};
+
+PyMODINIT_FUNC PyInit__packer(void) { return PyModule_Create(&module); }

@@ -27,6 +27,11 @@ import torch
 from . import _lib
 from .ops.cache_ops import _OnDevice, _stream_ptr
 
+try:  # the C packer (csrc/packer.c, built by lmserve_b200.build); pure-Python packing otherwise
+    from . import _packer
+except ImportError:  # pragma: no cover - depends on the build
+    _packer = None
+
 MAX_BATCH = 4096  # LMS_STEP_MAX_BATCH
 
 
@@ -70,6 +75,14 @@ def pack_requests(inputs: List, out: Optional[np.ndarray] = None
     batch = len(inputs)
     if batch > MAX_BATCH:
         raise ValueError(f"at most {MAX_BATCH} requests per step, got {batch}")
+    arrays = batch > 0 and all(isinstance(d.block_ids, np.ndarray) for d in inputs)
+    if _packer is not None and not arrays:
+        # one pass in C over the request objects, written straight into `out`
+        if out is None:
+            out = np.empty(4 * batch + sum(len(d.block_ids) + len(d.input_ids) for d in inputs),
+                           dtype=np.int32)
+        batch, T, NB, prefill_input_len, num_prefill, num_decode = _packer.pack(inputs, out)
+        return out[:4 * batch + NB + T], batch, T, NB, prefill_input_len, num_prefill, num_decode
     head = np.empty((4, batch), dtype=np.int32)
     prefill_input_len = num_prefill = num_decode = 0
     for b, data in enumerate(inputs):
@@ -100,7 +113,7 @@ def pack_requests(inputs: List, out: Optional[np.ndarray] = None
         packed = out[:n]
     packed[:4 * batch] = head.reshape(-1)
     o = 4 * batch
-    if batch and all(isinstance(d.block_ids, np.ndarray) for d in inputs):
+    if arrays:
         # block tables kept as arrays by the caller: no per-element conversion
         np.concatenate([d.block_ids for d in inputs], out=packed[o:o + total_blocks], casting="unsafe")
     else:

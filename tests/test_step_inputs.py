@@ -78,6 +78,40 @@ def test_pack_requests_layout_sort_and_validation():
         pack_requests(bad)
 
 
+def test_c_packer_and_python_packer_agree(monkeypatch):
+    import lmserve_b200.step_inputs as S
+    assert S._packer is not None, "lmserve_b200/_packer.so is not built (python -m lmserve_b200.build)"
+    reqs = W.make_step_requests(65536, 16, 70, 1, 900, 6, 129, 400, seed=44, spare_blocks=1)
+    reqs += [InferInput([], 0, 9, 9, [1, 2])]
+    fast = S.pack_requests(copy.deepcopy(reqs))
+    out = np.zeros(fast[0].size + 5, dtype=np.int32)
+    fast_into = S.pack_requests(copy.deepcopy(reqs), out)
+    monkeypatch.setattr(S, "_packer", None)
+    slow = S.pack_requests(copy.deepcopy(reqs))
+    for a in (fast, fast_into):
+        assert a[1:] == slow[1:]
+        assert np.array_equal(a[0], slow[0])
+    assert fast_into[0].base is out
+    # the C packer raises the same errors
+    monkeypatch.undo()
+    bad = hand_case()
+    bad[2].input_ids = []
+    with pytest.raises(ValueError, match="input ids"):
+        S.pack_requests(bad)
+    bad = hand_case()
+    bad[0].context_len = 99
+    with pytest.raises(ValueError, match="context_len - filled_token_len"):
+        S.pack_requests(bad)
+    bad = hand_case()
+    bad[0].block_ids = [1 << 40]
+    with pytest.raises(OverflowError):
+        S.pack_requests(bad)
+    with pytest.raises(ValueError, match="staging"):
+        S.pack_requests(hand_case(), np.zeros(13, dtype=np.int32))
+    with pytest.raises(AttributeError):
+        S.pack_requests([object()])
+
+
 def test_step_request_generator_is_consistent():
     reqs = W.make_step_requests(4096, 16, 12, 20, 300, 3, 64, 100, seed=5, spare_blocks=1)
     assert len(reqs) == 15
