@@ -149,7 +149,93 @@ done:
   return result;
 }
 
+/* flatten_dict(src_to_dst, out) -> n: writes the (src, dst) pairs of {src: [dst, ...]} - the
+ * argument of LMServe's copy_blocks (ops/cache_ops.py:8-15) - into the int64 buffer `out`
+ * ([n, 2], row-major) in the dict's iteration order.  ValueError if `out` is too small. */
+static PyObject* flatten_dict(PyObject* self, PyObject* args) {
+  PyObject* d;
+  Py_buffer out;
+  if (!PyArg_ParseTuple(args, "O!w*", &PyDict_Type, &d, &out)) return NULL;
+  int64_t* dst = (int64_t*)out.buf;
+  const Py_ssize_t cap = out.len / 16;
+  Py_ssize_t n = 0, pos = 0;
+  PyObject *key, *value;
+  PyObject* result = NULL;
+  while (PyDict_Next(d, &pos, &key, &value)) {
+    const long long src = PyLong_AsLongLong(key);
+    if (src == -1 && PyErr_Occurred()) goto done;
+    PyObject* fast = PySequence_Fast(value, "destinations must be a sequence of block ids");
+    if (!fast) goto done;
+    const Py_ssize_t m = PySequence_Fast_GET_SIZE(fast);
+    if (n + m > cap) {
+      Py_DECREF(fast);
+      PyErr_SetString(PyExc_ValueError, "pair buffer too small for the block map");
+      goto done;
+    }
+    PyObject** items = PySequence_Fast_ITEMS(fast);
+    for (Py_ssize_t i = 0; i < m; ++i) {
+      const long long dd = PyLong_AsLongLong(items[i]);
+      if (dd == -1 && PyErr_Occurred()) {
+        Py_DECREF(fast);
+        goto done;
+      }
+      dst[2 * (n + i)] = src;
+      dst[2 * (n + i) + 1] = dd;
+    }
+    n += m;
+    Py_DECREF(fast);
+  }
+  result = PyLong_FromSsize_t(n);
+done:
+  PyBuffer_Release(&out);
+  return result;
+}
+
+static int get_i64(PyObject* obj, PyObject* name, int64_t* out) {
+  PyObject* v = PyObject_GetAttr(obj, name);
+  if (!v) return -1;
+  const long long x = PyLong_AsLongLong(v);
+  Py_DECREF(v);
+  if (x == -1 && PyErr_Occurred()) return -1;
+  *out = x;
+  return 0;
+}
+
+/* flatten_entries(entries, out) -> n: (e.src_block_id, e.dst_block_id) of every entry of a
+ * BlockMapping (proto/worker.proto:78-86) into the int64 buffer `out` ([n, 2]). */
+static PyObject* flatten_entries(PyObject* self, PyObject* args) {
+  PyObject* entries;
+  Py_buffer out;
+  if (!PyArg_ParseTuple(args, "Ow*", &entries, &out)) return NULL;
+  PyObject* result = NULL;
+  PyObject* src_name = PyUnicode_InternFromString("src_block_id");
+  PyObject* dst_name = PyUnicode_InternFromString("dst_block_id");
+  PyObject* fast = PySequence_Fast(entries, "entries must be a sequence");
+  if (!fast || !src_name || !dst_name) goto done;
+  {
+    const Py_ssize_t n = PySequence_Fast_GET_SIZE(fast);
+    if (n > out.len / 16) {
+      PyErr_SetString(PyExc_ValueError, "pair buffer too small for the entries");
+      goto done;
+    }
+    int64_t* dst = (int64_t*)out.buf;
+    for (Py_ssize_t i = 0; i < n; ++i) {
+      PyObject* e = PySequence_Fast_GET_ITEM(fast, i);
+      if (get_i64(e, src_name, dst + 2 * i) || get_i64(e, dst_name, dst + 2 * i + 1)) goto done;
+    }
+    result = PyLong_FromSsize_t(n);
+  }
+done:
+  Py_XDECREF(fast);
+  Py_XDECREF(src_name);
+  Py_XDECREF(dst_name);
+  PyBuffer_Release(&out);
+  return result;
+}
+
 static PyMethodDef methods[] = {
+    {"flatten_dict", flatten_dict, METH_VARARGS, "flatten_dict(src_to_dst, out) -> number of pairs"},
+    {"flatten_entries", flatten_entries, METH_VARARGS, "flatten_entries(entries, out) -> number of pairs"},
     {"pack", pack, METH_VARARGS,
      "pack(inputs, out) -> (batch, total_tokens, total_blocks, prefill_input_len, num_prefill, num_decode)"},
     {NULL, NULL, 0, NULL}};

@@ -60,6 +60,10 @@ def mappings_to_pairs(block_mappings: Sequence) -> np.ndarray:
             continue
         entries = m.entries
         arr = np.empty((len(entries), 2), dtype=np.int64)
+        if cache_ops._packer is not None:
+            cache_ops._packer.flatten_entries(entries, arr)
+            chunks.append(arr)
+            continue
         for i, e in enumerate(entries):
             arr[i, 0] = e.src_block_id
             arr[i, 1] = e.dst_block_id

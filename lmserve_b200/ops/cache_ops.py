@@ -24,6 +24,11 @@ import torch
 
 from .. import _lib
 
+try:  # C helpers for walking Python containers (csrc/packer.c); pure Python otherwise
+    from .. import _packer
+except ImportError:  # pragma: no cover - depends on the build
+    _packer = None
+
 PairList = Union[Sequence[Tuple[int, int]], np.ndarray, torch.Tensor]
 
 
@@ -97,6 +102,14 @@ def flatten_block_map(src_to_dst: Union[Dict[int, Iterable[int]], PairList]) -> 
     ``BlockMapping.entries`` (``proto/worker.proto:78-86``).
     """
     if isinstance(src_to_dst, dict):
+        if _packer is not None:
+            try:
+                arr = np.empty((sum(map(len, src_to_dst.values())), 2), dtype=np.int64)
+            except TypeError:      # destinations given as iterators: no length to size the table by
+                arr = None
+            if arr is not None:
+                n = _packer.flatten_dict(src_to_dst, arr)
+                return arr[:n]
         flat = [x for src, dsts in src_to_dst.items() for dst in dsts for x in (src, dst)]
         return np.array(flat, dtype=np.int64).reshape(-1, 2)
     if isinstance(src_to_dst, torch.Tensor):

@@ -26,6 +26,28 @@ def test_flatten_block_map_matches_reference_order():
         cache_ops.flatten_block_map(np.zeros((2, 2), dtype=np.float32))
 
 
+def test_c_and_python_flatteners_agree(monkeypatch):
+    assert cache_ops._packer is not None, "lmserve_b200/_packer.so is not built (python -m lmserve_b200.build)"
+    rng = np.random.default_rng(3)
+    d = {int(s): [int(x) for x in rng.integers(0, 1 << 40, size=int(rng.integers(0, 9)))]
+         for s in rng.permutation(100)[:40]}
+    d[5] = (7, 8)                         # tuples and arrays as destination lists
+    d[6] = np.array([9, 10], dtype=np.int32)
+    ms = [BlockMapping([BlockMappingEntry(int(a), int(b)) for a, b in rng.integers(0, 1 << 31, size=(50, 2))]),
+          BlockMapping(), BlockMapping.from_pairs([(5, 6)])]
+    fast_d, fast_m = cache_ops.flatten_block_map(d), mappings_to_pairs(ms)
+    it = cache_ops.flatten_block_map({3: iter([4, 5])})      # no len(): handled without the C helper
+    monkeypatch.setattr(cache_ops, "_packer", None)
+    assert np.array_equal(fast_d, cache_ops.flatten_block_map(d))
+    assert np.array_equal(fast_m, mappings_to_pairs(ms))
+    assert it.tolist() == [[3, 4], [3, 5]]
+    monkeypatch.undo()
+    with pytest.raises(TypeError):
+        cache_ops.flatten_block_map({1: [2.5]})
+    with pytest.raises(TypeError):
+        cache_ops.flatten_block_map({"a": [2]})
+
+
 def test_mappings_to_pairs():
     ms = [BlockMapping([BlockMappingEntry(1, 2), BlockMappingEntry(3, 4)]), BlockMapping(),
           BlockMapping.from_pairs([(5, 6)])]
