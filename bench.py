@@ -442,6 +442,16 @@ def bench_prefill_cow(comm, stream, cache_view, dev, peak_gbs, sampler, small=Fa
     out["copy_blocks_cow"] = {"ms": ms, "bytes_compulsory": cb, "GB/s": cb / (ms * 1e-3) / 1e9,
                               "frac_of_hbm_peak": cb / (ms * 1e-3) / 1e9 / peak_gbs,
                               "GB/s_counting_every_read": 2 * len(w.pairs) * s.num_layers * s.chunk_bytes / (ms * 1e-3) / 1e9}
+    # the reference's call form: a {src: [dst, ...]} dict, flattened and uploaded inside the call
+    as_dict = {}
+    for src, dst in w.pairs.tolist():
+        as_dict.setdefault(src, []).append(dst)
+    ms_d = timed(comm, stream, lambda i: cache_ops.copy_blocks(kv, as_dict), n, 3, sampler) / n
+    t0 = time.perf_counter()
+    for _ in range(20):
+        cache_ops.flatten_block_map(as_dict)
+    out["copy_blocks_cow"]["ms_with_dict_argument"] = ms_d
+    out["copy_blocks_cow"]["host_us_to_flatten_the_dict"] = (time.perf_counter() - t0) / 20 * 1e6
     return out
 
 

@@ -347,11 +347,14 @@ class KVWorker:
                                self.chunk_bytes, [int(b) for b in block_ids]).serialize()
 
     def push_kv(self, peer_name: str, remote_descs: bytes, block_ids: Sequence[int],
-                stream: Optional[torch.cuda.Stream] = None) -> bool:
+                stream: Optional[torch.cuda.Stream] = None, post_events=None,
+                layers_per_launch: int = 1) -> bool:
         """Pushes local GPU blocks ``block_ids`` into the peer's reserved blocks
         (role of ``kv_worker.py:358-415``).  As there, surplus remote blocks are
         dropped so that both lists have ``len(block_ids)`` entries.  Returns False
-        (after printing the reason) instead of raising, like the reference."""
+        (after printing the reason) instead of raising, like the reference.  With
+        ``post_events`` (one event per layer, recorded by the model after it has written that
+        layer's KV) the push is issued layer by layer behind the prefill instead of after it."""
         try:
             desc = CacheDescriptor.deserialize(remote_descs)
             try:
@@ -364,8 +367,21 @@ class KVWorker:
                 if peer is None:
                     peer = PeerCache(desc)
                     self._peers[peer_name] = peer
-                with torch.cuda.stream(stream or self.push_stream):
-                    cache_ops.transfer_blocks(self.gpu_kv_caches, peer, pairs)
+                s = stream or self.push_stream
+                with torch.cuda.stream(s):
+                    if post_events is None:
+                        cache_ops.transfer_blocks(self.gpu_kv_caches, peer, pairs)
+                    else:
+                        # layer by layer behind the forward pass: layer l leaves as soon as the
+                        # model has recorded post_events[l] (the swap-out handshake, applied to
+                        # the push); the pair table is uploaded once
+                        table = cache_ops._pairs_on_device(pairs, self.device)
+                        step = max(1, int(layers_per_launch or 1))
+                        for l0 in range(0, self.num_layers, step):
+                            l1 = min(self.num_layers, l0 + step)
+                            for l in range(l0, l1):
+                                s.wait_event(post_events[l])
+                            cache_ops.transfer_blocks(self.gpu_kv_caches, peer, table, layers=(l0, l1))
             return True
         except _lib.LmsError as e:
             print(f"Posting transfer failed. {e}")

@@ -312,7 +312,7 @@ def test_pull_kv_from_another_process():
     prefill.close()
 
 
-def _pusher(desc_bytes, seed, pairs_src, q):
+def _pusher(desc_bytes, seed, pairs_src, q, layered=False):
     """Child process = the prefill-side worker: builds its own cache and pushes blocks into the
     parent's cache through the IPC descriptor."""
     try:
@@ -325,7 +325,14 @@ def _pusher(desc_bytes, seed, pairs_src, q):
         words = W.normal_words(np.random.default_rng(seed), shape.cache_shape, shape.dtype)
         cache = to_tensor(words, shape.dtype, "cuda:0")
         w = KVWorker("prefill0", cache)
-        ok = w.push_kv("decode0", desc_bytes, pairs_src)
+        if layered:
+            # the model's side of the handshake: one event per layer, recorded in layer order
+            events = [torch.cuda.Event() for _ in range(shape.num_layers)]
+            for e in events:
+                e.record()
+            ok = w.push_kv("decode0", desc_bytes, pairs_src, post_events=events, layers_per_launch=3)
+        else:
+            ok = w.push_kv("decode0", desc_bytes, pairs_src)
         w.push_stream.synchronize()
         w.close()
         q.put(("ok", ok))
@@ -333,9 +340,11 @@ def _pusher(desc_bytes, seed, pairs_src, q):
         q.put(("error", repr(e)))
 
 
-def test_push_kv_from_another_process():
+@pytest.mark.parametrize("layered", [False, True])
+def test_push_kv_from_another_process(layered):
     """get_descriptors on the decode side, push_kv from a second process (CUDA IPC mapping of
-    the destination cache), surplus remote blocks dropped as in the reference."""
+    the destination cache), surplus remote blocks dropped as in the reference; in one launch, and
+    layer by layer behind per-layer events."""
     shape = W.SHAPES["llama31_70b_tp8"].scaled(num_layers=4, num_blocks=64)
     dst_words, dst = make_gpu_cache(shape, 81)
     decode = KVWorker("decode0", dst)
@@ -345,7 +354,7 @@ def test_push_kv_from_another_process():
     torch.cuda.synchronize()
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    p = ctx.Process(target=_pusher, args=(desc, 82, src_blocks, q))
+    p = ctx.Process(target=_pusher, args=(desc, 82, src_blocks, q, layered))
     p.start()
     status, payload = q.get(timeout=300)
     p.join(timeout=60)
