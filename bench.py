@@ -347,6 +347,9 @@ def run_ours(args):
             if torch.cuda.device_count() >= 2 and "transfer_local" in ops_wanted:
                 extra(["transfer_local"], lambda: bench_transfer_local(comm, stream, cache_view, dev,
                                                                        args, sampler))
+            if "write_scaling" in ops_wanted:
+                extra(["write_scaling"], lambda: bench_write_scaling(comm, stream, cache_view, dev, peak_gbs,
+                                                                     args, sampler))
             if "flashinfer" in ops_wanted:
                 extra(["flashinfer"], lambda: bench_vs_flashinfer(comm, stream, cache_view, dev, args, sampler))
         extra(["tp8"], lambda: bench_tp8_decode(comm, stream, cache_view, dev, rank, world, peak_gbs,
@@ -847,6 +850,48 @@ def bench_vs_flashinfer(comm, stream, cache_view, dev, args, sampler):
     return {"vs_flashinfer_per_layer_decode_write": out}
 
 
+def bench_write_scaling(comm, stream, cache_view, dev, peak_gbs, args, sampler):
+    """Decode-step write against the size of the step: the all-layer launch for 128 ... 2048
+    tokens of the Llama-3.1-70B TP8 shard (256-byte rows, 80 layers) and of Llama-3.1-8B
+    (2 KiB rows, 32 layers), steps replayed back to back from CUDA graphs.  Separates the fixed
+    cost of a launch from the streaming rate.  Not part of --ops all."""
+    from lmserve_b200.ops import cache_ops
+    out = {}
+    for name, shape_key, tokens, ctx in (("tp8_256B_rows_80_layers", "llama31_70b_tp8", (128, 256, 512, 1024, 2048), (512, 1024)),
+                                         ("8b_2KiB_rows_32_layers", "llama31_8b", (64, 128, 256, 512), (128, 1024))):
+        s = W.SHAPES[shape_key]
+        kv = cache_view(s)
+        rows = []
+        for T in tokens:
+            wl = [W.make_decode_write(s, T, ctx[0], ctx[1], seed=7005 + 31 * i) for i in range(ROTATE)]
+            keys = [torch.randn(s.num_layers, T, s.num_kv_heads, s.head_dim, device=dev, dtype=torch.bfloat16)
+                    for _ in range(ROTATE)]
+            vals = [torch.randn_like(k) for k in keys]
+            slots = [torch.from_numpy(w.slot_mapping).to(dev) for w in wl]
+            plans = [cache_ops.WritePlan(keys[j], vals[j], kv, slots[j]) for j in range(ROTATE)]
+            side = torch.cuda.Stream()
+            side.wait_stream(stream)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                cs = torch.cuda.current_stream().cuda_stream
+                for j in range(GRAPH_STEPS):
+                    plans[j % ROTATE].run(cs)
+            stream.wait_stream(side)
+            torch.cuda.synchronize()
+            ms = min(timed(comm, stream, lambda i: g.replay(), 5, 2, sampler) for _ in range(3)) / (5 * GRAPH_STEPS)
+            b = wl[0].algorithmic_bytes()
+            rows.append({"tokens": T, "MiB": b / 2**20, "us_per_step": ms * 1e3,
+                         "GB/s": b / (ms * 1e-3) / 1e9, "frac_of_hbm_peak": b / (ms * 1e-3) / 1e9 / peak_gbs})
+            del plans, keys, vals, g
+        # least-squares line us = fixed + bytes / rate over the sizes measured
+        x = np.array([r["MiB"] * 2**20 for r in rows])
+        y = np.array([r["us_per_step"] for r in rows])
+        slope, fixed = np.polyfit(x, y, 1)
+        out[name] = {"steps": rows, "fit_fixed_us_per_launch": float(fixed),
+                     "fit_streaming_GB/s": float(1.0 / slope / 1e3)}
+    return {"decode_write_vs_step_size": out}
+
+
 def bench_tp8_decode(comm, stream, cache_view, dev, rank, world, peak_gbs, args, sampler):
     """Llama-3.1-70B under TP=8: one KV head per GPU (256-byte rows), 80 layers, batch 512."""
     from lmserve_b200.ops import cache_ops
@@ -1060,7 +1105,8 @@ def main():
     ap.add_argument("--ops", default="all",
                     help="comma list of extra workloads: all, none, prefill_cow, swap, rope, index_prep, tp8, "
                          "transfer (multi-rank), transfer_local (two GPUs in one process; not in 'all'), "
-                         "flashinfer (comparison with flashinfer.append_paged_kv_cache; not in 'all')")
+                         "flashinfer (comparison with flashinfer.append_paged_kv_cache; not in 'all'), "
+                         "write_scaling (decode write against step size; not in 'all')")
     ap.add_argument("--host-pool-gib", type=float, default=32.0,
                     help="cap of the pinned host pool of the swap workload")
     ap.add_argument("--no-cpu-baseline", action="store_true")
