@@ -221,6 +221,72 @@ class KVWorkerParams:
                    [e.ipc_handle() for e in pre_events], [e.ipc_handle() for e in post_events])
 
 
+def cache_block_counts(gpu_cache_size: int, host_cache_size: int, num_layers: int, num_kv_heads: int,
+                       head_dim: int, block_size: int, dtype: torch.dtype):
+    """``(num_gpu_blocks, num_host_blocks, kv_block_size)`` with the arithmetic of
+    ``ModelWorker.init_cache`` (``model_worker.py:215-220,278-279``): ``kv_block_size`` is the
+    bytes of the K (or V) half of one block of one layer, and a block costs
+    ``num_layers * 2 * kv_block_size`` bytes in either pool."""
+    dtype_byte = torch.finfo(dtype).bits // 8
+    kv_block_size = block_size * num_kv_heads * head_dim * dtype_byte
+    per_block = num_layers * 2 * kv_block_size
+    return int(gpu_cache_size) // per_block, int(host_cache_size) // per_block, kv_block_size
+
+
+@dataclass
+class KVWorkerHandle:
+    """The model process's end of the layer handshake: ``KVWorkerHandle`` of ``kv_worker.py:25-32``
+    without its two wake-up queues (the events order the streams by themselves).  Layer ``i`` of
+    the forward pass waits for ``pre_events[i]`` (its blocks have been swapped in) and records
+    ``post_events[i]`` when it has written its KV (they may be swapped out or pushed)."""
+    pre_events: List[torch.cuda.Event]
+    post_events: List[torch.cuda.Event]
+    enable_wait_before_execute: bool = False
+    enable_record_after_execute: bool = False
+
+    def register_hooks(self, attn_layers, stream: Optional[torch.cuda.Stream] = None) -> list:
+        """Forward pre / post hooks on the attention modules, as ``model_worker.py:253-275``:
+        the pre-hook makes `stream` (default: the current stream) wait for the layer's
+        pre-event when ``enable_wait_before_execute`` is set, the post-hook records the layer's
+        post-event when ``enable_record_after_execute`` is set.  Returns the hook handles."""
+        handles = []
+        for i, layer in enumerate(attn_layers):
+            def pre_hook(mod, args, i=i):
+                if self.enable_wait_before_execute:
+                    (stream or torch.cuda.current_stream()).wait_event(self.pre_events[i])
+
+            def post_hook(mod, args, output, i=i):
+                if self.enable_record_after_execute:
+                    self.post_events[i].record(stream or torch.cuda.current_stream())
+
+            handles.append(layer.register_forward_pre_hook(pre_hook))
+            handles.append(layer.register_forward_hook(post_hook))
+        return handles
+
+
+def init_cache(gpu_cache_size: int, host_cache_size: int, *, num_layers: int, num_kv_heads: int,
+               head_dim: int, block_size: int, dtype: torch.dtype, device="cuda"):
+    """``ModelWorker.init_cache`` (``model_worker.py:200-308``) for the GPU and host tiers:
+    allocates the paged cache ``[L, num_gpu_blocks, 2, block_size, H, D]``, creates the per-layer
+    interprocess events, and returns ``(kv_caches, handle, params)`` — the cache for the model,
+    the :class:`KVWorkerHandle` for its hooks, and the :class:`KVWorkerParams` to send to the KV
+    process (``KVWorker.from_params``)."""
+    num_gpu_blocks, num_host_blocks, _ = cache_block_counts(
+        gpu_cache_size, host_cache_size, num_layers, num_kv_heads, head_dim, block_size, dtype)
+    if num_gpu_blocks <= 0:
+        raise ValueError("gpu_cache_size is smaller than one block")
+    dev = torch.device(device)
+    if dev.type != "cuda":
+        raise RuntimeError("the KV cache lives on a CUDA device; there is no CPU path")
+    with torch.cuda.device(dev):
+        kv_caches = torch.empty(num_layers, num_gpu_blocks, 2, block_size, num_kv_heads, head_dim,
+                                dtype=dtype, device=dev)
+        pre = [torch.cuda.Event(interprocess=True) for _ in range(num_layers)]
+        post = [torch.cuda.Event(interprocess=True) for _ in range(num_layers)]
+    handle = KVWorkerHandle(pre, post)
+    return kv_caches, handle, KVWorkerParams.from_cache(kv_caches, num_host_blocks, pre, post)
+
+
 class KVWorker:
     """Per-GPU mover of KV blocks, API-compatible with the GPU-facing part of LMServe's
     ``KVWorker`` (``kv_worker.py:88-195,249-295,336-415``).

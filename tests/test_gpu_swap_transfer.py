@@ -29,7 +29,7 @@ def make_gpu_cache(shape, seed):
     return words, to_tensor(words, shape.dtype, DEV)
 
 
-@pytest.mark.parametrize("variant", [0, 1, 2, 3])
+@pytest.mark.parametrize("variant", [0, 1, 2, 3, 4])
 @pytest.mark.parametrize("ctas", [0, 8, 300])
 def test_swap_out_in_vs_oracle(ctas, variant):
     L = _lib.lib()
@@ -187,7 +187,7 @@ def test_kvworker_copy_kv_with_layer_events():
         worker.close()
 
 
-@pytest.mark.parametrize("variant", [0, 1, 2, 3])
+@pytest.mark.parametrize("variant", [0, 1, 2, 3, 4])
 def test_transfer_blocks_same_device_vs_oracle(variant):
     _lib.lib().lms_set_tuning(_lib.TUNE_XFER_VARIANT, variant)
     shape = W.SHAPES["llama31_70b_tp8"].scaled(num_layers=6, num_blocks=300)
@@ -268,6 +268,60 @@ def test_kv_process_maps_the_model_process_cache_and_events():
     assert payload == int(hw[out_pairs[:, 1]].view(np.uint8).astype(np.int64).sum())
     cache_oracle.swap_in(gw, hw, in_pairs)
     assert np.array_equal(to_words(gpu).reshape(gw.shape), gw)
+
+
+def test_init_cache_and_layer_hooks_drive_the_swap_handshake():
+    """init_cache sizes and allocates the cache as the reference does; the forward hooks record
+    post_events after each attention layer has written its KV and make a layer wait for its
+    pre_event, and the KV worker's per-layer swaps are ordered by exactly those events."""
+    from lmserve_b200.kv_worker import BlockMapping, init_cache
+    L_, H, D, BS = 3, 2, 64, 16
+    per_block = L_ * 2 * BS * H * D * 2
+    kv, handle, params = init_cache(per_block * 12 + 100, per_block * 5, num_layers=L_, num_kv_heads=H,
+                                    head_dim=D, block_size=BS, dtype=torch.float16, device=DEV)
+    assert kv.shape == (L_, 12, 2, BS, H, D) and params.num_host_blocks == 5
+    assert params.cache_shape == tuple(kv.shape) and len(params.pre_event_handles) == L_
+    kv.zero_()
+
+    class Attention(torch.nn.Module):
+        def __init__(self, layer):
+            super().__init__()
+            self.layer = layer
+
+        def forward(self, x):
+            seen = kv[self.layer, 7].clone()          # what the layer finds in block 7
+            kv[self.layer, 3] = x + self.layer         # the KV this layer produces, in block 3
+            return seen
+
+    layers = torch.nn.ModuleList(Attention(i) for i in range(L_))
+    handle.register_hooks(layers)
+    worker = KVWorker("kv0", kv, num_host_blocks=5)
+    side = torch.cuda.Stream()
+    try:
+        # forward pass that records post_events; the worker saves block 3 layer by layer behind it
+        handle.enable_record_after_execute = True
+        x = torch.full((2, BS, H, D), 2.0, dtype=torch.float16, device=DEV)
+        for layer in layers:
+            layer(x)
+        worker.save_kv_blocks_to_host([BlockMapping.from_pairs([(3, 4)])], stream=side,
+                                      post_events=handle.post_events)
+        side.synchronize()
+        got = worker.host_pool.array.view(np.float16).reshape(5, L_, -1)
+        for l in range(L_):
+            assert (got[4, l] == 2.0 + l).all()
+        # the worker loads host block 4 into GPU block 7 and signals pre_events; the layers wait
+        handle.enable_record_after_execute = False
+        handle.enable_wait_before_execute = True
+        worker.load_kv_blocks_from_host([BlockMapping.from_pairs([(4, 7)])], stream=side,
+                                        pre_events=handle.pre_events)
+        seen = [layer(x) for layer in layers]
+        torch.cuda.synchronize()
+        for l in range(L_):
+            assert (seen[l] == 2.0 + l).all()
+    finally:
+        worker.close()
+    with pytest.raises(ValueError, match="smaller than one block"):
+        init_cache(10, 0, num_layers=L_, num_kv_heads=H, head_dim=D, block_size=BS, dtype=torch.float16, device=DEV)
 
 
 def _puller(desc_bytes, seed, local_blocks, q):
@@ -367,7 +421,7 @@ def test_push_kv_from_another_process(layered):
     decode.close()
 
 
-@pytest.mark.parametrize("variant", [0, 1, 2, 3])
+@pytest.mark.parametrize("variant", [0, 1, 2, 3, 4])
 def test_chunk_ops_do_not_touch_memory_around_their_buffers(variant):
     """copy_blocks, swap-in and transfer run on caches that are slices of larger buffers; the
     guard blocks before and after (and the host pool's neighbours) must come out unchanged,

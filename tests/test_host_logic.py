@@ -48,6 +48,17 @@ def test_c_and_python_flatteners_agree(monkeypatch):
         cache_ops.flatten_block_map({"a": [2]})
 
 
+def test_cache_block_counts_follow_the_reference_arithmetic():
+    from lmserve_b200.kv_worker import cache_block_counts
+    # Llama-3.1-8B: 32 layers, 8 KV heads of 128, block 16, bf16 -> 32 KiB per K (or V) half,
+    # 2 MiB per block over all layers (model_worker.py:215-220)
+    g, h, kvb = cache_block_counts(128 << 30, 256 << 30, 32, 8, 128, 16, torch.bfloat16)
+    assert (g, h, kvb) == (65536, 131072, 32768)
+    g, h, kvb = cache_block_counts((2 << 20) * 7 + 5, 0, 32, 8, 128, 16, torch.float16)
+    assert (g, h) == (7, 0)
+    assert cache_block_counts(100, 100, 1, 8, 64, 16, torch.float16)[:2] == (0, 0)
+
+
 def test_mappings_to_pairs():
     ms = [BlockMapping([BlockMappingEntry(1, 2), BlockMappingEntry(3, 4)]), BlockMapping(),
           BlockMapping.from_pairs([(5, 6)])]
