@@ -207,6 +207,8 @@ class KVWorkerParams:
     device_index: int = 0
     pre_event_handles: Sequence[bytes] = ()
     post_event_handles: Sequence[bytes] = ()
+    num_disk_blocks: int = 0
+    disk_kv_cache_file: Optional[str] = None
 
     @classmethod
     def from_cache(cls, kv_caches: torch.Tensor, num_host_blocks: int = 0,
@@ -287,6 +289,25 @@ def init_cache(gpu_cache_size: int, host_cache_size: int, *, num_layers: int, nu
     return kv_caches, handle, KVWorkerParams.from_cache(kv_caches, num_host_blocks, pre, post)
 
 
+def open_disk_pool(path: str, shape) -> np.ndarray:
+    """The disk tier's block pool ``[num_disk_blocks, L, chunk_bytes]`` as a writable ``.npy``
+    memory map (role of ``memmap_disk_kv_cache``, ``kv_worker.py:48-84``): an existing file of the
+    right shape is reused, anything else is replaced by a new file.  Payload is held as bytes."""
+    import os
+    shape = tuple(int(x) for x in shape)
+    if os.path.exists(path):
+        try:
+            arr = np.load(path, mmap_mode="r+")
+            if arr.shape == shape and arr.dtype == np.uint8:
+                return arr
+            del arr
+        except Exception:  # noqa: BLE001 - an unreadable file is replaced, as in the reference
+            pass
+        os.remove(path)
+    os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
+    return np.lib.format.open_memmap(path, mode="w+", dtype=np.uint8, shape=shape)
+
+
 class KVWorker:
     """Per-GPU mover of KV blocks, API-compatible with the GPU-facing part of LMServe's
     ``KVWorker`` (``kv_worker.py:88-195,249-295,336-415``).
@@ -296,7 +317,8 @@ class KVWorker:
     """
 
     def __init__(self, name: str, gpu_kv_caches: torch.Tensor, num_host_blocks: int = 0,
-                 swap_engine: str = "kernel"):
+                 swap_engine: str = "kernel", num_disk_blocks: int = 0,
+                 disk_kv_cache_file: Optional[str] = None, num_disk_copy_workers: int = 4):
         cache_ops._require_cuda("gpu_kv_caches", gpu_kv_caches)
         if swap_engine not in ("kernel", "dma"):
             raise ValueError("swap_engine must be 'kernel' or 'dma'")
@@ -322,6 +344,19 @@ class KVWorker:
             (Device.GPU, Device.Host): self.save_kv_blocks_to_host,
             (Device.Host, Device.GPU): self.load_kv_blocks_from_host,
         }
+        # Disk tier (kv_worker.py:131-139,229-247,296-322): a host-only path, no GPU involved -
+        # blocks move between the pinned pool and a memory-mapped .npy file, one task per layer.
+        self.disk_kv_caches = None
+        self._disk_threads = None
+        if num_disk_blocks > 0:
+            if self.host_pool is None or not disk_kv_cache_file:
+                raise ValueError("the disk tier needs a host pool and a disk_kv_cache_file")
+            from concurrent.futures import ThreadPoolExecutor
+            self.disk_kv_caches = open_disk_pool(
+                disk_kv_cache_file, (num_disk_blocks, self.num_layers, self.chunk_bytes))
+            self._disk_threads = ThreadPoolExecutor(max_workers=max(1, int(num_disk_copy_workers)))
+            self.COPY_KV_OP_MAP[(Device.Host, Device.Disk)] = self.save_kv_blocks_to_disk
+            self.COPY_KV_OP_MAP[(Device.Disk, Device.Host)] = self.load_kv_blocks_from_disk
 
     @classmethod
     def from_params(cls, name: str, params: KVWorkerParams) -> "KVWorker":
@@ -334,7 +369,8 @@ class KVWorker:
             cache = torch.empty(0, dtype=params.dtype, device=dev)
             cache.set_(storage)
             cache = cache.view(*params.cache_shape)
-            worker = cls(name, cache, params.num_host_blocks)
+            worker = cls(name, cache, params.num_host_blocks, num_disk_blocks=params.num_disk_blocks,
+                         disk_kv_cache_file=params.disk_kv_cache_file)
             worker.pre_events = [torch.cuda.Event.from_ipc_handle(dev, h) for h in params.pre_event_handles]
             worker.post_events = [torch.cuda.Event.from_ipc_handle(dev, h) for h in params.post_event_handles]
         return worker
@@ -363,6 +399,31 @@ class KVWorker:
         """
         self._swap(block_mappings, "out", stream or self.dtoh_stream, None, post_events,
                    layers_per_launch)
+
+    def _disk_copy(self, block_mappings, dst, src, wait_for) -> None:
+        pairs = mappings_to_pairs(block_mappings)
+        if pairs.shape[0] == 0:
+            return
+        for name, ids, pool in (("source", pairs[:, 0], src), ("destination", pairs[:, 1], dst)):
+            if ids.min() < 0 or ids.max() >= pool.shape[0]:
+                raise IndexError(f"{name} block id outside the pool of {pool.shape[0]} blocks")
+        for stream in wait_for:      # swaps in flight on the pinned pool must have landed / left
+            stream.synchronize()
+        s_ids, d_ids = pairs[:, 0], pairs[:, 1]
+
+        def one_layer(l):
+            dst[d_ids, l] = src[s_ids, l]
+
+        list(self._disk_threads.map(one_layer, range(self.num_layers)))
+
+    def save_kv_blocks_to_disk(self, block_mappings) -> None:
+        """Host -> disk (``kv_worker.py:239-247,311-322``): ``disk[dst, l] = host[src, l]``."""
+        self._disk_copy(block_mappings, self.disk_kv_caches, self.host_pool.array, (self.dtoh_stream,))
+
+    def load_kv_blocks_from_disk(self, block_mappings) -> None:
+        """Disk -> host (``kv_worker.py:229-237,296-309``): ``host[dst, l] = disk[src, l]``."""
+        self._disk_copy(block_mappings, self.host_pool.array, self.disk_kv_caches,
+                        (self.dtoh_stream, self.htod_stream))
 
     def _swap(self, block_mappings, direction, stream, pre_events, post_events, group) -> None:
         if self.host_pool is None:
@@ -491,6 +552,12 @@ class KVWorker:
         for p in self._peers.values():
             p.close()
         self._peers.clear()
+        if self._disk_threads is not None:
+            self._disk_threads.shutdown(wait=True)
+            self._disk_threads = None
+        if self.disk_kv_caches is not None:
+            self.disk_kv_caches.flush()
+            self.disk_kv_caches = None
         if self.host_pool is not None:
             self.host_pool.close()
             self.host_pool = None

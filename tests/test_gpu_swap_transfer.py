@@ -324,6 +324,37 @@ def test_init_cache_and_layer_hooks_drive_the_swap_handshake():
         init_cache(10, 0, num_layers=L_, num_kv_heads=H, head_dim=D, block_size=BS, dtype=torch.float16, device=DEV)
 
 
+def test_disk_tier_round_trip_through_copy_kv(tmp_path):
+    """GPU -> host -> disk -> host -> GPU through KVWorker.copy_kv, the four directions of the
+    reference's dispatch table; the disk file is a .npy memory map."""
+    from lmserve_b200.kv_worker import BlockMapping, Device
+    shape = W.SHAPES["llama31_8b_swap"].scaled(num_layers=3, num_blocks=32, num_kv_heads=2)
+    words, gpu = make_gpu_cache(shape, 91)
+    f = str(tmp_path / "disk-kv-cache-0.npy")
+    worker = KVWorker("kv0", gpu, num_host_blocks=6, num_disk_blocks=10, disk_kv_cache_file=f)
+    try:
+        m = lambda pairs: [BlockMapping.from_pairs(pairs)]
+        worker.copy_kv(m([(4, 0), (9, 5), (31, 2)]), Device.GPU, Device.Host)
+        worker.copy_kv(m([(0, 7), (5, 1), (2, 9)]), Device.Host, Device.Disk)
+        worker.host_pool.array[...] = 0
+        worker.copy_kv(m([(7, 3), (9, 4)]), Device.Disk, Device.Host)
+        worker.copy_kv(m([(3, 20), (4, 21)]), Device.Host, Device.GPU)
+        torch.cuda.synchronize()
+        gw = words.reshape(3, 32, -1)
+        got = to_words(gpu).reshape(gw.shape)
+        assert np.array_equal(got[:, 20], gw[:, 4]) and np.array_equal(got[:, 21], gw[:, 31])
+        disk = np.load(f, mmap_mode="r")
+        assert np.array_equal(disk[1].view(np.uint16), gw[:, 9])
+        with pytest.raises(ValueError, match="Unsupported copy direction"):
+            worker.copy_kv(m([(0, 0)]), Device.GPU, Device.Disk)
+        with pytest.raises(IndexError):
+            worker.copy_kv(m([(0, 10)]), Device.Host, Device.Disk)
+    finally:
+        worker.close()
+    with pytest.raises(ValueError, match="disk tier needs"):
+        KVWorker("kv1", gpu, num_host_blocks=0, num_disk_blocks=2, disk_kv_cache_file=f)
+
+
 def _puller(desc_bytes, seed, local_blocks, q):
     """Child = the decode-side worker pulling blocks out of the parent's (prefill) cache."""
     try:

@@ -59,6 +59,25 @@ def test_cache_block_counts_follow_the_reference_arithmetic():
     assert cache_block_counts(100, 100, 1, 8, 64, 16, torch.float16)[:2] == (0, 0)
 
 
+def test_disk_pool_file_is_reused_or_replaced(tmp_path):
+    from lmserve_b200.kv_worker import open_disk_pool
+    f = str(tmp_path / "sub" / "disk-kv-cache-0.npy")
+    a = open_disk_pool(f, (4, 2, 64))
+    assert a.shape == (4, 2, 64) and a.dtype == np.uint8
+    a[1, 1, :] = 7
+    a.flush()
+    del a
+    b = open_disk_pool(f, (4, 2, 64))            # same geometry: contents survive
+    assert (b[1, 1] == 7).all()
+    del b
+    c = open_disk_pool(f, (5, 2, 64))            # geometry changed: a new, empty file
+    assert c.shape == (5, 2, 64) and not c.any()
+    del c
+    (tmp_path / "junk.npy").write_bytes(b"not an npy file")
+    d = open_disk_pool(str(tmp_path / "junk.npy"), (1, 1, 16))
+    assert d.shape == (1, 1, 16)
+
+
 def test_mappings_to_pairs():
     ms = [BlockMapping([BlockMappingEntry(1, 2), BlockMappingEntry(3, 4)]), BlockMapping(),
           BlockMapping.from_pairs([(5, 6)])]
