@@ -230,6 +230,12 @@ int lms_append_paged_kv_cache(const void* key, const void* value,
  *                           + positions[i] % block_size, or -1 when that page is not in the
  *                           request's table (reported as LMS_ERR_INDEX with debug checks on)
  *   input_ids[i]          = token_ids[i] widened to int64
+ *   decode_kv_block_indptrs[d] = kv_block_indptrs[num_prefill+d] - kv_block_indptrs[num_prefill],
+ *                           d = 0..num_decode: the page-table offsets of the decode requests
+ *                           alone (requests [num_prefill, num_prefill+num_decode) of the sorted
+ *                           batch), which the reference builds a second time for its decode
+ *                           attention plan (build_decode_wrapper, model_worker.py:83-140); the
+ *                           prefill requests' arrays are prefixes of the batch arrays
  * total_tokens must equal the sum of input_len and total_blocks the sum of num_blocks.
  * batch <= LMS_STEP_MAX_BATCH, else LMS_ERR_TOO_LARGE.
  */
@@ -242,7 +248,8 @@ int lms_build_step_indices(const int32_t* input_len, const int32_t* filled_len,
                            int32_t* cu_seqlens_q, int32_t* kv_block_indptrs,
                            int32_t* kv_block_indices, int32_t* kv_last_block_lens,
                            int32_t* batch_indices, int32_t* positions,
-                           int64_t* slot_mapping, int64_t* input_ids, void* stream);
+                           int64_t* slot_mapping, int64_t* input_ids, int32_t num_prefill,
+                           int32_t num_decode, int32_t* decode_kv_block_indptrs, void* stream);
 
 /*
  * Rotary position embedding, optionally fused with the cache write that follows it in the

@@ -75,7 +75,7 @@ SIGNATURES = {
     "lms_build_step_indices": (c_int, [
         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int64, c_int64,
         c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-        c_void_p, c_void_p, c_void_p]),
+        c_void_p, c_void_p, c_int32, c_int32, c_void_p, c_void_p]),
     "lms_copy_blocks": (c_int, [
         c_void_p, c_int64, c_int64, c_int64, c_int32, c_void_p, c_int64, c_int64, c_void_p]),
     "lms_swap_blocks": (c_int, [

@@ -591,20 +591,24 @@ int lms_build_step_indices(const int32_t* input_len, const int32_t* filled_len,
                            int32_t* cu_seqlens_q, int32_t* kv_block_indptrs,
                            int32_t* kv_block_indices, int32_t* kv_last_block_lens,
                            int32_t* batch_indices, int32_t* positions,
-                           int64_t* slot_mapping, int64_t* input_ids, void* stream) {
+                           int64_t* slot_mapping, int64_t* input_ids, int32_t num_prefill,
+                           int32_t num_decode, int32_t* decode_kv_block_indptrs, void* stream) {
+  if (num_prefill < 0 || num_decode < 0 || (int64_t)num_prefill + num_decode > batch)
+    return LMS_ERR_RANGE;
   if (batch < 0 || total_tokens < 0 || total_blocks < 0 || block_size <= 0 ||
       total_tokens > 0x7fffffffll || total_blocks > 0x7fffffffll)
     return LMS_ERR_RANGE;
   if (batch > LMS_STEP_MAX_BATCH) return LMS_ERR_TOO_LARGE;
   // An empty step still defines cu_seqlens_q[0] = kv_block_indptrs[0] = 0.
-  if (batch == 0 && total_tokens == 0 && total_blocks == 0 && !cu_seqlens_q && !kv_block_indptrs)
+  if (batch == 0 && total_tokens == 0 && total_blocks == 0 && !cu_seqlens_q && !kv_block_indptrs &&
+      !decode_kv_block_indptrs)
     return LMS_OK;
   if (batch > 0 && (!input_len || !filled_len || !context_len || !num_blocks)) return LMS_ERR_NULL;
   if (total_blocks > 0 && !block_ids) return LMS_ERR_NULL;
   if (input_ids && total_tokens > 0 && !token_ids) return LMS_ERR_NULL;
   const void* four[] = {input_len, filled_len, context_len, num_blocks, block_ids, token_ids,
                         position_ids, cu_seqlens_q, kv_block_indptrs, kv_block_indices,
-                        kv_last_block_lens, batch_indices, positions};
+                        kv_last_block_lens, batch_indices, positions, decode_kv_block_indptrs};
   for (const void* q : four)
     if (((uintptr_t)q & 3u) != 0) return LMS_ERR_ALIGN;
   if (((uintptr_t)slot_mapping & 7u) != 0 || ((uintptr_t)input_ids & 7u) != 0) return LMS_ERR_ALIGN;
@@ -631,6 +635,9 @@ int lms_build_step_indices(const int32_t* input_len, const int32_t* filled_len,
   p.positions = positions;
   p.slot_mapping = (long long*)slot_mapping;
   p.input_ids = (long long*)input_ids;
+  p.decode_kv_block_indptrs = decode_kv_block_indptrs;
+  p.num_prefill = num_prefill;
+  p.num_decode = num_decode;
   p.err = ds->err.load(std::memory_order_relaxed);
   p.checks = g_checks.load(std::memory_order_relaxed);
   LMS_CUDA(launch_step_indices(p, ds->sms, (cudaStream_t)stream));

@@ -138,6 +138,10 @@ struct StepIndexParams {
   int* positions;           // [total_tokens]
   long long* slot_mapping;  // [total_tokens]
   long long* input_ids;     // [total_tokens]
+  // Page-table offsets of the decode requests alone (requests [num_prefill, num_prefill +
+  // num_decode) of the sorted batch), rebased to start at 0: [num_decode + 1]
+  int* decode_kv_block_indptrs;
+  int num_prefill, num_decode;
   ErrRecord* err;
   int checks;
 };

@@ -45,7 +45,8 @@ static int copy_ints(PyObject* fast, Py_ssize_t n, int32_t* dst, const char* wha
   return 0;
 }
 
-/* pack(inputs, out) -> (batch, total_tokens, total_blocks, prefill_input_len, num_prefill, num_decode)
+/* pack(inputs, out) -> (batch, total_tokens, total_blocks, prefill_input_len, num_prefill, num_decode,
+ *                       prefill_blocks, decode_blocks)
  * `out` is a writable, C-contiguous buffer of int32 (a numpy array); ValueError when it is too
  * small or when a request is inconsistent, with the messages of the pure-Python packer. */
 static PyObject* pack(PyObject* self, PyObject* args) {
@@ -78,6 +79,7 @@ static PyObject* pack(PyObject* self, PyObject* args) {
       goto done;
     }
     long long total_tokens = 0, total_blocks = 0, prefill_len = 0, n_pre = 0, n_dec = 0;
+    long long prefill_blocks = 0, decode_blocks = 0;
     for (Py_ssize_t b = 0; b < batch; ++b) {
       PyObject* r = PySequence_Fast_GET_ITEM(reqs, b);
       int32_t q, filled, ctx;
@@ -105,13 +107,15 @@ static PyObject* pack(PyObject* self, PyObject* args) {
                      (long long)ctx - filled, (int)q);
         goto done;
       }
+      const Py_ssize_t nb = PySequence_Fast_GET_SIZE(blocks[b]);
       if (q > 1) {
         prefill_len += q;
         ++n_pre;
+        prefill_blocks += nb;
       } else if (q == 1) {
         ++n_dec;
+        decode_blocks += nb;
       }
-      const Py_ssize_t nb = PySequence_Fast_GET_SIZE(blocks[b]);
       buf[b] = q;
       buf[batch + b] = filled;
       buf[2 * batch + b] = ctx;
@@ -135,7 +139,8 @@ static PyObject* pack(PyObject* self, PyObject* args) {
       if (copy_ints(ids[b], n, dst, "input_ids")) goto done;
       dst += n;
     }
-    result = Py_BuildValue("(nLLLLL)", batch, total_tokens, total_blocks, prefill_len, n_pre, n_dec);
+    result = Py_BuildValue("(nLLLLLLL)", batch, total_tokens, total_blocks, prefill_len, n_pre, n_dec,
+                           prefill_blocks, decode_blocks);
   }
 done:
   if (blocks)
@@ -237,7 +242,8 @@ static PyMethodDef methods[] = {
     {"flatten_dict", flatten_dict, METH_VARARGS, "flatten_dict(src_to_dst, out) -> number of pairs"},
     {"flatten_entries", flatten_entries, METH_VARARGS, "flatten_entries(entries, out) -> number of pairs"},
     {"pack", pack, METH_VARARGS,
-     "pack(inputs, out) -> (batch, total_tokens, total_blocks, prefill_input_len, num_prefill, num_decode)"},
+     "pack(inputs, out) -> (batch, total_tokens, total_blocks, prefill_input_len, num_prefill, num_decode, "
+     "prefill_blocks, decode_blocks)"},
     {NULL, NULL, 0, NULL}};
 
 static struct PyModuleDef module = {PyModuleDef_HEAD_INIT, "_packer",

@@ -20,6 +20,8 @@
 //     slot_mapping[i]      = block_ids[kv_block_indptrs[b] + positions[i] / block_size] * block_size
 //                            + positions[i] % block_size        (-1 if the page is not in the table)
 //   kv_block_indices[j]    = block_ids[j];  input_ids[i] = (int64) token_ids[i]
+//   decode_kv_block_indptrs[d] = kv_block_indptrs[num_prefill + d] - kv_block_indptrs[num_prefill]
+//                            (the page table of the decode requests alone, for their attention plan)
 //
 // Every CTA scans the (small) per-request arrays into shared memory by itself, so there is no
 // grid-wide dependency; CTA 0 also writes the per-request outputs.  Tokens find their request
@@ -86,6 +88,8 @@ __global__ void __launch_bounds__(kThreads) step_indices_kernel(const StepIndexP
       if (p.kv_block_indptrs) p.kv_block_indptrs[b] = indptr[b];
       if (b < p.batch && p.kv_last_block_lens)
         p.kv_last_block_lens[b] = floor_mod(p.context_len[b] - 1, p.block_size) + 1;
+      if (p.decode_kv_block_indptrs && b >= p.num_prefill && b <= p.num_prefill + p.num_decode)
+        p.decode_kv_block_indptrs[b - p.num_prefill] = indptr[b] - indptr[p.num_prefill];
     }
   }
 

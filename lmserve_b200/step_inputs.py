@@ -47,6 +47,16 @@ class InferInput:
 
 
 @dataclass
+class PagedArrays:
+    """The arrays one flashinfer attention plan takes (``prefill_wrapper.plan`` /
+    ``decode_wrapper.plan``, ``model_worker.py:68-79,126-137``) for one phase of the batch."""
+    qo_indptr: Optional[torch.Tensor]      # int32 [n + 1]; None for decode (one token per request)
+    kv_indptr: torch.Tensor                # int32 [n + 1], starting at 0
+    kv_indices: torch.Tensor               # int32
+    kv_last_page_len: torch.Tensor         # int32 [n]
+
+
+@dataclass
 class StepIndices:
     """Index tensors of one step; names as in ``InputParams`` plus ``slot_mapping``."""
     position_ids: torch.Tensor        # int32 [T]
@@ -60,16 +70,21 @@ class StepIndices:
     slot_mapping: torch.Tensor        # int64 [T]
     num_prefill: int = 0
     num_decode: int = 0
+    # the same page table split by phase, as the reference rebuilds it for its two attention
+    # wrappers (build_prefill_wrapper / build_decode_wrapper, ``model_worker.py:20-140``); the
+    # batch is sorted prefill first, so these are views (decode offsets rebased on the device)
+    prefill: Optional[PagedArrays] = None
+    decode: Optional[PagedArrays] = None
 
 
-def pack_requests(inputs: List, out: Optional[np.ndarray] = None
-                  ) -> Tuple[np.ndarray, int, int, int, int, int, int]:
+def pack_requests(inputs: List, out: Optional[np.ndarray] = None) -> tuple:
     """Sort `inputs` as the reference does and pack them into one int32 array (`out`, if it is
     given and large enough — a ValueError otherwise — else a new array).
 
     Layout: ``[input_len | filled_len | context_len | num_blocks]`` (each `batch` long), then the
     concatenated block ids, then the token ids.  Returns ``(packed, batch, total_tokens,
-    total_blocks, prefill_input_len, num_prefill, num_decode)``.
+    total_blocks, prefill_input_len, num_prefill, num_decode, prefill_blocks, decode_blocks)``;
+    the last two are the block-table entries of the prefill and of the decode requests.
     """
     inputs.sort(key=lambda x: -x.input_len)
     batch = len(inputs)
@@ -81,10 +96,10 @@ def pack_requests(inputs: List, out: Optional[np.ndarray] = None
         if out is None:
             out = np.empty(4 * batch + sum(len(d.block_ids) + len(d.input_ids) for d in inputs),
                            dtype=np.int32)
-        batch, T, NB, prefill_input_len, num_prefill, num_decode = _packer.pack(inputs, out)
-        return out[:4 * batch + NB + T], batch, T, NB, prefill_input_len, num_prefill, num_decode
+        batch, T, NB, prefill_input_len, num_prefill, num_decode, pb, db = _packer.pack(inputs, out)
+        return out[:4 * batch + NB + T], batch, T, NB, prefill_input_len, num_prefill, num_decode, pb, db
     head = np.empty((4, batch), dtype=np.int32)
-    prefill_input_len = num_prefill = num_decode = 0
+    prefill_input_len = num_prefill = num_decode = prefill_blocks = decode_blocks = 0
     for b, data in enumerate(inputs):
         q = int(data.input_len)
         if len(data.input_ids) != q:
@@ -96,8 +111,10 @@ def pack_requests(inputs: List, out: Optional[np.ndarray] = None
         if q > 1:
             prefill_input_len += q
             num_prefill += 1
+            prefill_blocks += len(data.block_ids)
         elif q == 1:
             num_decode += 1
+            decode_blocks += len(data.block_ids)
         head[0, b] = q
         head[1, b] = data.filled_token_len
         head[2, b] = data.context_len
@@ -122,7 +139,8 @@ def pack_requests(inputs: List, out: Optional[np.ndarray] = None
     o += total_blocks
     packed[o:o + total_tokens] = np.fromiter(
         chain.from_iterable(d.input_ids for d in inputs), dtype=np.int32, count=total_tokens)
-    return packed, batch, total_tokens, total_blocks, prefill_input_len, num_prefill, num_decode
+    return (packed, batch, total_tokens, total_blocks, prefill_input_len, num_prefill, num_decode,
+            prefill_blocks, decode_blocks)
 
 
 class StepInputBuilder:
@@ -154,8 +172,9 @@ class StepInputBuilder:
         with torch.cuda.device(self.device):
             self._in = torch.empty(n_in, dtype=torch.int32, device=self.device)
             # int32 outputs: position_ids, batch_indices, positions [T each]; cu_q, indptr [B+1];
-            # last_lens [B]; kv_block_indices [NB].  int64 outputs: slot_mapping, input_ids [T].
-            self._out32 = torch.empty(3 * self.max_tokens + 3 * self.max_batch + 2 + self.max_blocks,
+            # last_lens [B]; decode indptr [B+1]; kv_block_indices [NB].  int64 outputs:
+            # slot_mapping, input_ids [T].
+            self._out32 = torch.empty(3 * self.max_tokens + 4 * self.max_batch + 3 + self.max_blocks,
                                       dtype=torch.int32, device=self.device)
             self._out64 = torch.empty(2 * self.max_tokens, dtype=torch.int64, device=self.device)
             _lib.check(_lib.lib().lms_init_device())
@@ -166,7 +185,7 @@ class StepInputBuilder:
         self._turn = (turn + 1) % len(self._staging)
         if self._used[turn]:
             self._copied[turn].synchronize()
-        packed, batch, T, NB, prefill_len, n_pre, n_dec = pack_requests(inputs, self._staging_np[turn])
+        packed, batch, T, NB, prefill_len, n_pre, n_dec, pb, db = pack_requests(inputs, self._staging_np[turn])
         if T > self.max_tokens or NB > self.max_blocks or batch > self.max_batch:
             raise ValueError(
                 f"step of {batch} requests / {T} tokens / {NB} block-table entries exceeds the "
@@ -176,9 +195,9 @@ class StepInputBuilder:
             self._in[:n].copy_(self._staging[turn][:n], non_blocking=True)
             self._copied[turn].record()
             self._used[turn] = True
-            return self._launch(batch, T, NB, prefill_len, n_pre, n_dec)
+            return self._launch(batch, T, NB, prefill_len, n_pre, n_dec, pb, db)
 
-    def _launch(self, batch, T, NB, prefill_len, n_pre, n_dec):
+    def _launch(self, batch, T, NB, prefill_len, n_pre, n_dec, pb=0, db=0):
         i32, i64 = self._out32, self._out64
         mt, mb = self.max_tokens, self.max_batch
         position_ids = i32[0:T]
@@ -188,7 +207,8 @@ class StepInputBuilder:
         cu_q = i32[o:o + batch + 1]
         indptr = i32[o + mb + 1:o + mb + 1 + batch + 1]
         last = i32[o + 2 * mb + 2:o + 2 * mb + 2 + batch]
-        kv_idx = i32[o + 3 * mb + 2:o + 3 * mb + 2 + NB]
+        dec_indptr = i32[o + 3 * mb + 2:o + 3 * mb + 2 + n_dec + 1]
+        kv_idx = i32[o + 4 * mb + 3:o + 4 * mb + 3 + NB]
         slot_mapping = i64[0:T]
         input_ids = i64[mt:mt + T]
         base = self._in.data_ptr()
@@ -197,12 +217,15 @@ class StepInputBuilder:
             base + 16 * batch, base + 16 * batch + 4 * NB, batch, T, NB, self.block_size,
             position_ids.data_ptr(), cu_q.data_ptr(), indptr.data_ptr(), kv_idx.data_ptr(),
             last.data_ptr(), batch_indices.data_ptr(), positions.data_ptr(),
-            slot_mapping.data_ptr(), input_ids.data_ptr(), _stream_ptr(self.device)))
+            slot_mapping.data_ptr(), input_ids.data_ptr(), n_pre, n_dec, dec_indptr.data_ptr(),
+            _stream_ptr(self.device)))
         return input_ids, StepIndices(
             position_ids=position_ids, cu_seqlens_q=cu_q, prefill_input_len=prefill_len,
             batch_indices=batch_indices, positions=positions, kv_block_indices=kv_idx,
             kv_block_indptrs=indptr, kv_last_block_lens=last, slot_mapping=slot_mapping,
-            num_prefill=n_pre, num_decode=n_dec)
+            num_prefill=n_pre, num_decode=n_dec,
+            prefill=PagedArrays(cu_q[:n_pre + 1], indptr[:n_pre + 1], kv_idx[:pb], last[:n_pre]) if n_pre else None,
+            decode=PagedArrays(None, dec_indptr, kv_idx[pb:pb + db], last[n_pre:n_pre + n_dec]) if n_dec else None)
 
 
 def make_inputs(inputs: List, block_size: int, device,

@@ -54,8 +54,8 @@ def test_oracle_on_a_case_worked_by_hand():
 
 def test_pack_requests_layout_sort_and_validation():
     inputs = hand_case()
-    packed, batch, T, NB, prefill_len, n_pre, n_dec = pack_requests(inputs)
-    assert (batch, T, NB, prefill_len, n_pre, n_dec) == (3, 6, 5, 4, 1, 2)
+    packed, batch, T, NB, prefill_len, n_pre, n_dec, pb, db = pack_requests(inputs)
+    assert (batch, T, NB, prefill_len, n_pre, n_dec, pb, db) == (3, 6, 5, 4, 1, 2, 2, 3)
     assert packed.dtype == np.int32
     assert packed.tolist() == [4, 1, 1, 14, 16, 2, 18, 17, 3, 2, 2, 1,
                                3, 8, 5, 9, 6, 1, 2, 3, 4, 7, 11]
@@ -130,13 +130,14 @@ def test_step_request_generator_is_consistent():
 def test_argument_errors_need_no_gpu():
     lib = _lib.lib()
     z = [None] * 6
-    outs = [None] * 9
+    outs = [None] * 9 + [0, 0, None]
     assert lib.lms_build_step_indices(*z, -1, 0, 0, 16, *outs, None) == _lib.LMS_ERR_RANGE
     assert lib.lms_build_step_indices(*z, 0, 0, 0, 0, *outs, None) == _lib.LMS_ERR_RANGE
     assert lib.lms_build_step_indices(*z, 4097, 1, 1, 16, *outs, None) == _lib.LMS_ERR_TOO_LARGE
     assert lib.lms_build_step_indices(*z, 0, 0, 0, 16, *outs, None) == _lib.LMS_OK
     assert lib.lms_build_step_indices(*z, 2, 2, 2, 16, *outs, None) == _lib.LMS_ERR_NULL
     assert lib.lms_build_step_indices(16, 16, 16, 16, 18, 16, 2, 2, 2, 16, *outs, None) == _lib.LMS_ERR_ALIGN
+    assert lib.lms_build_step_indices(*z, 2, 2, 2, 16, *([None] * 9), 2, 1, None, None) == _lib.LMS_ERR_RANGE
 
 
 # ------------------------------------------------------------------ GPU: kernel vs oracle
@@ -148,6 +149,39 @@ def run_builder(reqs, block_size=16, **kw):
     got["input_ids"] = ids.cpu().numpy()
     got["prefill_input_len"] = s.prefill_input_len
     return got, s
+
+
+def phase_arrays(reqs, page_size):
+    """The page table of the prefill and of the decode requests alone, built the way
+    build_prefill_wrapper / build_decode_wrapper do (model_worker.py:30-63, 94-124)."""
+    reqs = sorted(reqs, key=lambda x: -x.input_len)
+    out = {}
+    for name, sel in (("prefill", [d for d in reqs if d.input_len > 1]),
+                      ("decode", [d for d in reqs if d.input_len == 1])):
+        if not sel:
+            out[name] = None
+            continue
+        out[name] = dict(
+            qo_indptr=np.cumsum([0] + [d.input_len for d in sel]).astype(np.int32),
+            kv_indptr=np.cumsum([0] + [len(d.block_ids) for d in sel]).astype(np.int32),
+            kv_indices=np.asarray([b for d in sel for b in d.block_ids], dtype=np.int32),
+            kv_last_page_len=np.asarray([(d.context_len - 1) % page_size + 1 for d in sel], dtype=np.int32))
+    return out
+
+
+def assert_phases(s, reqs, page_size=16):
+    want = phase_arrays(reqs, page_size)
+    for name in ("prefill", "decode"):
+        got = getattr(s, name)
+        if want[name] is None:
+            assert got is None
+            continue
+        for f in ("kv_indptr", "kv_indices", "kv_last_page_len"):
+            assert np.array_equal(getattr(got, f).cpu().numpy(), want[name][f]), (name, f)
+        if name == "prefill":
+            assert np.array_equal(got.qo_indptr.cpu().numpy(), want[name]["qo_indptr"])
+        else:
+            assert got.qo_indptr is None
 
 
 def assert_same(got, want):
@@ -172,8 +206,9 @@ STEP_CASES = {
 def test_kernel_matches_oracle(name):
     reqs = W.make_step_requests(65536, 16, seed=31 + len(name), **STEP_CASES[name])
     want = step_oracle.make_inputs(copy.deepcopy(reqs), 16)
-    got, _ = run_builder(reqs)
+    got, s = run_builder(copy.deepcopy(reqs))
     assert_same(got, want)
+    assert_phases(s, reqs)
 
 
 @pytest.mark.gpu
@@ -183,8 +218,9 @@ def test_hand_case_requests_without_tokens_and_other_block_sizes():
     # requests with no new token keep their table entries and are stepped over by the tokens
     reqs = hand_case() + [InferInput([], 0, 40, 40, [21, 22, 23]), InferInput([], 0, 5, 5, [30])]
     reqs = [reqs[3], reqs[0], reqs[4], reqs[1], reqs[2]]
-    got, _ = run_builder(copy.deepcopy(reqs))
+    got, s = run_builder(copy.deepcopy(reqs))
     assert_same(got, step_oracle.make_inputs(copy.deepcopy(reqs), 16))
+    assert_phases(s, reqs)       # requests without new tokens belong to neither phase
     for bs in (1, 8, 24, 32):
         reqs = W.make_step_requests(4096, bs, 17, 1, 200, 3, 50, 70, seed=bs)
         got, _ = run_builder(copy.deepcopy(reqs), block_size=bs)
