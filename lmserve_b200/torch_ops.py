@@ -24,7 +24,6 @@ from __future__ import annotations
 
 from types import SimpleNamespace
 
-import torch
 from torch import Tensor
 from torch.library import custom_op
 

@@ -196,6 +196,7 @@ STEP_CASES = {
     "mixed": dict(num_decode=100, ctx_lo=1, ctx_hi=700, num_prefill=9, chunk_tokens=512, max_offset=3000),
     "prefill64": dict(num_decode=0, ctx_lo=0, ctx_hi=0, num_prefill=64, chunk_tokens=512, max_offset=8192),
     "many_requests": dict(num_decode=3000, ctx_lo=1, ctx_hi=90, num_prefill=57, chunk_tokens=33, max_offset=50),
+    "max_batch": dict(num_decode=4090, ctx_lo=1, ctx_hi=40, num_prefill=6, chunk_tokens=17, max_offset=30),
     "spare_blocks": dict(num_decode=40, ctx_lo=5, ctx_hi=400, num_prefill=4, chunk_tokens=100, max_offset=64,
                          spare_blocks=2),
 }
