@@ -973,12 +973,24 @@ def bench_transfer(comm, stream, cache_view, dev, rank, world, sampler):
     reps = 3
     ms = timed(comm, stream, fn, reps, 2, sampler) / reps
     ms_dma = timed(comm, stream, dma, reps, 2, sampler) / reps
+    # the mirror image (KVWorker.pull_kv): the decode GPU runs the kernel and loads the same
+    # blocks out of the prefill GPU's cache over NVLink
+    if role == "decode":
+        src = PeerCache(CacheDescriptor.deserialize(descs[peer]))
+        pairs = torch.from_numpy(w.pairs).to(dev)
+        pull = lambda i: cache_ops.transfer_blocks(src, kv, pairs, pull=True)
+    else:
+        pull = lambda i: None
+    ms_pull = timed(comm, stream, pull, reps, 2, sampler) / reps
     if role == "prefill":
         pc.close()
+    else:
+        src.close()
     pairs_n = world // 2
     gbs = nbytes / (ms * 1e-3) / 1e9
     dma_gbs = (1 << 30) / (ms_dma * 1e-3) / 1e9
     return {"prefill_to_decode_transfer": {
+        "pull_ms": ms_pull, "pull_GB/s_per_pair": nbytes / (ms_pull * 1e-3) / 1e9,
         "ms": ms, "bytes_per_pair": nbytes, "pairs": pairs_n, "GB/s_per_pair": gbs,
         "GB/s_all_pairs": gbs * pairs_n, "nvlink_peer_copy_GB/s_measured_memcpy": dma_gbs,
         "frac_of_measured_peer_copy": gbs / dma_gbs, "frac_of_nominal_900": gbs / 900.0}}

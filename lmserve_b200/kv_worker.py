@@ -536,13 +536,8 @@ class KVWorker:
                     print("Creating transfer failed. cache geometries differ")
                     return False
                 table = np.ascontiguousarray(pairs[:, ::-1])              # (remote src, local dst)
-                s = stream or self.push_stream
-                with torch.cuda.stream(s):
-                    _lib.check(_lib.lib().lms_transfer_blocks_host(
-                        peer.device_ptr, peer.layer_stride, peer.block_stride,
-                        self.gpu_kv_caches.data_ptr(), self.layer_stride, self.block_stride,
-                        self.chunk_bytes, self.num_layers, table.ctypes.data, len(table),
-                        peer.num_blocks, self.num_gpu_blocks, s.cuda_stream))
+                with torch.cuda.stream(stream or self.push_stream):
+                    cache_ops.transfer_blocks(peer, self.gpu_kv_caches, table, pull=True)
             return True
         except _lib.LmsError as e:
             print(f"Posting transfer failed. {e}")

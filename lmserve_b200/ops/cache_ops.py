@@ -557,36 +557,44 @@ def swap_blocks(
 
 
 def transfer_blocks(
-    src_kv_caches: torch.Tensor,
+    src_kv_caches,
     dst_kv_caches,
     block_pairs: PairList,
     layers: Optional[Tuple[int, int]] = None,
+    pull: bool = False,
 ) -> None:
-    """Pushes blocks of the local cache into a peer GPU's cache: ``dst[:, d] = src[:, s]``.
+    """Moves blocks of one GPU's cache into another GPU's cache: ``dst[:, d] = src[:, s]``.
 
-    Replaces the host-staged NIXL push of ``kv_worker.py:358-415`` with one
-    kernel on the source GPU storing over NVLink.  ``dst_kv_caches`` is either a
-    tensor on another device of this process (peer access is enabled on demand)
-    or a :class:`lmserve_b200.kv_worker.PeerCache` opened from another
-    process's IPC handle.  Runs on the source device's current stream.  ``layers=(begin, end)``
-    pushes only that layer range, so a prefill worker can ship each layer as soon as it is
-    computed instead of waiting for the whole forward pass.
+    Replaces the host-staged NIXL push of ``kv_worker.py:358-415`` with one kernel over NVLink.
+    One side is a tensor of this process, the other a tensor on another device of this process
+    (peer access is enabled on demand) or a :class:`lmserve_b200.kv_worker.PeerCache` opened
+    from another process's IPC handle.  By default the kernel runs on the *source* GPU and
+    stores into the peer (a push, ``src_kv_caches`` local); with ``pull=True`` it runs on the
+    *destination* GPU and loads from the peer (``dst_kv_caches`` local) — over NVLink the loads
+    are the faster direction (788 against 715 GB/s for the 2.5 GiB transfer of the 70B TP8
+    shard).  Runs on the current stream of the GPU that executes the kernel.
+    ``layers=(begin, end)`` moves only that layer range, so a prefill worker can ship each
+    layer as soon as it is computed instead of waiting for the whole forward pass.
     """
-    _require_cuda("src_kv_caches", src_kv_caches)
-    dev = src_kv_caches.device
-    L, NB, s_layer, s_block, chunk = _cache_geometry(src_kv_caches)
-    if isinstance(dst_kv_caches, torch.Tensor):
-        _require_cuda("dst_kv_caches", dst_kv_caches)
-        dL, dNB, d_layer, d_block, d_chunk = _cache_geometry(dst_kv_caches)
-        dst_ptr = dst_kv_caches.data_ptr()
-        if dst_kv_caches.device != dev:
-            with _OnDevice(dev):
-                _lib.check(_lib.lib().lms_peer_enable(dst_kv_caches.device.index))
-    else:
-        dL, dNB, d_layer, d_block, d_chunk = (dst_kv_caches.num_layers, dst_kv_caches.num_blocks,
-                                              dst_kv_caches.layer_stride, dst_kv_caches.block_stride,
-                                              dst_kv_caches.chunk_bytes)
-        dst_ptr = dst_kv_caches.device_ptr
+    def geometry(c):
+        if isinstance(c, torch.Tensor):
+            _require_cuda("kv_caches", c)
+            L_, NB_, layer, block, chunk_ = _cache_geometry(c)
+            return L_, NB_, layer, block, chunk_, c.data_ptr(), c.device
+        return (c.num_layers, c.num_blocks, c.layer_stride, c.block_stride, c.chunk_bytes,
+                c.device_ptr, None)
+
+    local = dst_kv_caches if pull else src_kv_caches
+    if not isinstance(local, torch.Tensor):
+        raise TypeError("the cache on the GPU that runs the kernel must be a tensor of this process "
+                        f"({'dst' if pull else 'src'}_kv_caches)")
+    L, NB, s_layer, s_block, chunk, src_ptr, src_dev = geometry(src_kv_caches)
+    dL, dNB, d_layer, d_block, d_chunk, dst_ptr, dst_dev = geometry(dst_kv_caches)
+    dev = local.device
+    other = src_dev if pull else dst_dev
+    if other is not None and other != dev:
+        with _OnDevice(dev):
+            _lib.check(_lib.lib().lms_peer_enable(other.index))
     if dL != L or d_chunk != chunk:
         raise ValueError("source and destination caches must have the same layers and chunk size")
     l0, l1 = (0, L) if layers is None else layers
@@ -598,6 +606,6 @@ def transfer_blocks(
     L_ = _lib.lib()
     fn = L_.lms_transfer_blocks if on_device else L_.lms_transfer_blocks_host
     with _OnDevice(dev):
-        _lib.check(fn(src_kv_caches.data_ptr() + l0 * s_layer, s_layer, s_block,
+        _lib.check(fn(src_ptr + l0 * s_layer, s_layer, s_block,
                       dst_ptr + l0 * d_layer, d_layer, d_block,
                       chunk, l1 - l0, ptr, n, NB, dNB, _stream_ptr(dev)))

@@ -216,6 +216,32 @@ def test_transfer_blocks_across_devices():
     want = dst_words.copy()
     cache_oracle.transfer(src_words, want, tr.pairs)
     assert np.array_equal(to_words(dst), want)
+    # the same transfer pulled: the kernel runs on cuda:1 and loads from cuda:0
+    dst2 = to_tensor(dst_words, shape.dtype, "cuda:1")
+    torch.cuda.synchronize("cuda:1")
+    cache_ops.transfer_blocks(src, dst2, tr.pairs, pull=True)
+    torch.cuda.synchronize("cuda:1")
+    assert np.array_equal(to_words(dst2), want)
+    assert np.array_equal(to_words(src), src_words)
+
+
+def test_transfer_blocks_pull_on_one_device_and_argument_errors():
+    shape = W.SHAPES["llama31_70b_tp8"].scaled(num_layers=3, num_blocks=40)
+    src_words, src = make_gpu_cache(shape, 77)
+    dst_words, dst = make_gpu_cache(shape, 78)
+    pairs = np.array([[1, 5], [2, 39], [30, 0]], dtype=np.int64)
+    cache_ops.transfer_blocks(src, dst, pairs, pull=True, layers=(1, 3))
+    torch.cuda.synchronize()
+    want = dst_words.copy()
+    cache_oracle.transfer(src_words[1:3], want[1:3], pairs)
+    assert np.array_equal(to_words(dst), want)
+
+    class NotATensor:
+        num_layers, num_blocks, layer_stride, block_stride, chunk_bytes, device_ptr = 3, 40, 0, 0, 0, 0
+    with pytest.raises(TypeError, match="dst_kv_caches"):
+        cache_ops.transfer_blocks(src, NotATensor(), pairs, pull=True)
+    with pytest.raises(TypeError, match="src_kv_caches"):
+        cache_ops.transfer_blocks(NotATensor(), dst, pairs)
 
 
 def _kv_process(params, out_pairs, in_pairs, q):
