@@ -941,7 +941,22 @@ def bench_transfer_local(comm, stream, cache_view, dev, args, sampler):
     reps = 3
     ms = timed(comm, stream, lambda i: cache_ops.transfer_blocks(src, dst, pairs), reps, 2, sampler) / reps
     torch.cuda.synchronize("cuda:1")
-    return {"transfer_local": {"ms": ms, "bytes": tr.bytes(), "GB/s": tr.bytes() / (ms * 1e-3) / 1e9}}
+    # the same blocks pulled: the kernel runs on cuda:1 and loads from cuda:0
+    with torch.cuda.device(1):
+        pairs1 = pairs.to("cuda:1")
+        s1 = torch.cuda.current_stream()
+        for _ in range(2):
+            cache_ops.transfer_blocks(src, dst, pairs1, pull=True)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(s1)
+        for _ in range(reps):
+            cache_ops.transfer_blocks(src, dst, pairs1, pull=True)
+        e1.record(s1)
+        torch.cuda.synchronize()
+        ms_pull = e0.elapsed_time(e1) / reps
+    return {"transfer_local": {"ms": ms, "bytes": tr.bytes(), "GB/s": tr.bytes() / (ms * 1e-3) / 1e9,
+                               "pull_ms": ms_pull, "pull_GB/s": tr.bytes() / (ms_pull * 1e-3) / 1e9}}
 
 
 def bench_transfer(comm, stream, cache_view, dev, rank, world, sampler):
