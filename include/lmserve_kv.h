@@ -65,7 +65,9 @@ typedef enum lms_status {
                                     3 = untiled one-vector-per-thread, 4 = persistent 16-byte with
                                     1024-thread CTAs (128 KiB in flight per CTA, for grids of a few CTAs) */
 #define LMS_TUNE_COPY_CTAS_PER_SM 4
-#define LMS_TUNE_SWAP_OUT_CTAS 5 /* total CTAs of the GPU->host kernel */
+#define LMS_TUNE_SWAP_OUT_CTAS 5 /* total CTAs of the GPU->host kernel; built-in 3 (of 1024 threads), which
+                                    fills a PCIe Gen5 x16 link and leaves the SMs to concurrent GEMMs -
+                                    raise it on a faster host link */
 #define LMS_TUNE_SWAP_IN_CTAS 6  /* total CTAs of the host->GPU kernel */
 #define LMS_TUNE_XFER_CTAS_PER_SM 7
 #define LMS_TUNE_XFER_VARIANT 8  /* as LMS_TUNE_COPY_VARIANT */
