@@ -1,7 +1,8 @@
 /*
  * The C ABI used from plain C99, without Python or PyTorch: allocates a small paged cache
  * with the CUDA runtime, writes rows through lms_reshape_and_cache, duplicates blocks with
- * lms_copy_blocks_host, and checks the bytes on the host.  Built and run by
+ * lms_copy_blocks_host, derives a step's index arrays with lms_build_step_indices, and checks
+ * everything on the host.  Built and run by
  * tests/test_c_abi_from_c.py; exit code 0 = all checks passed.
  */
 #include <cuda_runtime_api.h>
@@ -61,6 +62,31 @@ int main(void) {
   /* argument errors come back as statuses */
   if (lms_reshape_and_cache(key + 1, value, ROW, ROW, cache, cache, chunk, ROW, slots, T, ROW, BS, 0, NULL) != LMS_ERR_ALIGN) ++bad;
   if (lms_copy_blocks_host(cache, NB * chunk, chunk, chunk, 1, NULL, 2, NB, NULL) != LMS_ERR_NULL) ++bad;
+  {
+    /* three requests, sorted by descending input_len: a 4-token prefill chunk (14 cached
+       tokens, blocks 3 and 8), a decode at position 16 (blocks 5, 9), a decode at position 2
+       (block 6); page size 16 */
+    enum { B = 3, TOK = 6, NBLK = 5 };
+    const int32_t h_in[4 * B + NBLK] = {4, 1, 1, 14, 16, 2, 18, 17, 3, 2, 2, 1, 3, 8, 5, 9, 6};
+    const int64_t want_slots[TOK] = {3 * 16 + 14, 3 * 16 + 15, 8 * 16, 8 * 16 + 1, 9 * 16, 6 * 16 + 2};
+    const int32_t want_cu[B + 1] = {0, 4, 5, 6};
+    int32_t *d_in, *d_cu, h_cu[B + 1];
+    int64_t *d_slots, h_out[TOK];
+    CHECK_CUDA(cudaMalloc((void**)&d_in, sizeof h_in));
+    CHECK_CUDA(cudaMalloc((void**)&d_cu, sizeof h_cu));
+    CHECK_CUDA(cudaMalloc((void**)&d_slots, sizeof h_out));
+    CHECK_CUDA(cudaMemcpy(d_in, h_in, sizeof h_in, cudaMemcpyHostToDevice));
+    CHECK_LMS(lms_build_step_indices(d_in, d_in + B, d_in + 2 * B, d_in + 3 * B, d_in + 4 * B, NULL,
+                                     B, TOK, NBLK, 16, NULL, d_cu, NULL, NULL, NULL, NULL, NULL,
+                                     d_slots, NULL, 1, 2, NULL, NULL));
+    CHECK_CUDA(cudaMemcpy(h_out, d_slots, sizeof h_out, cudaMemcpyDeviceToHost));
+    CHECK_CUDA(cudaMemcpy(h_cu, d_cu, sizeof h_cu, cudaMemcpyDeviceToHost));
+    if (memcmp(h_out, want_slots, sizeof h_out) || memcmp(h_cu, want_cu, sizeof h_cu)) ++bad;
+    if (lms_build_step_indices(d_in, d_in + B, d_in + 2 * B, d_in + 3 * B, d_in + 4 * B, NULL,
+                               LMS_STEP_MAX_BATCH + 1, TOK, NBLK, 16, NULL, d_cu, NULL, NULL, NULL,
+                               NULL, NULL, d_slots, NULL, 0, 0, NULL, NULL) != LMS_ERR_TOO_LARGE) ++bad;
+    cudaFree(d_in); cudaFree(d_cu); cudaFree(d_slots);
+  }
   printf("c abi demo: %s, %lld launches\n", bad ? "FAILED" : "ok", (long long)lms_launch_count());
   cudaFree(cache); cudaFree(key); cudaFree(value); cudaFree(slots);
   return bad ? 4 : 0;

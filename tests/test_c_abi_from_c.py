@@ -43,4 +43,4 @@ def test_library_runs_from_plain_c(tmp_path):
     assert res.returncode == 0, res.stderr
     run = subprocess.run([str(exe)], capture_output=True, text=True, timeout=120)
     assert run.returncode == 0, run.stdout + run.stderr
-    assert "c abi demo: ok, 2 launches" in run.stdout
+    assert "c abi demo: ok, 3 launches" in run.stdout
