@@ -2,8 +2,12 @@
 
 ``lmserve_b200.ops`` mirrors ``llm_worker.ops`` (``copy_blocks``,
 ``fill_key_cache`` and the paged/interleaved ``reshape_and_cache``);
-``lmserve_b200.kv_worker`` mirrors the GPU-facing part of ``llm_worker.kv_worker``.
-All device work is done by ``liblmserve_kv.so`` (C ABI: ``include/lmserve_kv.h``).
+``lmserve_b200.kv_worker`` mirrors ``llm_worker.kv_worker`` (swap, push / pull, cache
+allocation and the per-layer event handshake), ``lmserve_b200.step_inputs`` the per-step index
+preparation of ``ModelWorker._make_inputs``, ``lmserve_b200.kv_service`` the ``worker.KVWorker``
+gRPC service; ``lmserve_b200.torch_ops`` registers the operators as ``torch.ops.lmserve_cache.*``.
+All device work is done by ``liblmserve_kv.so`` (C ABI: ``include/lmserve_kv.h``); there is no
+CPU fallback.
 """
 from . import _lib
 from .ops import (copy_blocks, fill_key_cache, reshape_and_cache,
