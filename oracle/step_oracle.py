@@ -9,8 +9,9 @@ definitions (flashinfer-python, pinned at 0.3.1.post1 by the reference's lock fi
     batch_indices = request index of every appended token
     positions     = seq_lens[b] - (append_indptr[b+1] - append_indptr[b]) + offset in the request
 
-Pins: the worked example in the ``get_batch_indices_positions`` documentation (checked in the
-CPU tests), and, on a GPU box, flashinfer's own functions (checked in the GPU tests).  The slot
+Pins: the worked example in the ``get_batch_indices_positions`` documentation and vectors made
+by flashinfer's own functions on a B200 (``tests/golden/step_indices_flashinfer.npz``), both
+checked in the CPU tests; on a GPU box the installed flashinfer functions are called as well.  The slot
 mapping is this build's addition: ``block_ids[pos // BS] * BS + pos % BS`` per request.
 """
 from __future__ import annotations

@@ -27,6 +27,25 @@ def test_oracle_matches_the_documented_flashinfer_example():
     assert step_oracle.get_seq_lens(np.array([0, 3, 3, 4]), np.array([5, 16, 1]), 16).tolist() == [37, 16, 1]
 
 
+def test_oracle_matches_vectors_made_by_flashinfer_on_a_gpu():
+    """tests/golden/step_indices_flashinfer.npz: flashinfer.get_seq_lens and
+    get_batch_indices_positions run on a B200 on a seeded request list
+    (tests/golden/make_step_golden.py); the oracle reproduces them from the same list."""
+    import importlib.util
+    from helpers import GOLDEN
+    spec = importlib.util.spec_from_file_location("make_step_golden", GOLDEN / "make_step_golden.py")
+    gen = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(gen)
+    z = np.load(GOLDEN / "step_indices_flashinfer.npz")
+    reqs = W.make_step_requests(**gen.GENERATOR)
+    o = step_oracle.make_inputs(reqs, gen.GENERATOR["block_size"])
+    assert np.array_equal(o["batch_indices"], z["batch_indices"])
+    assert np.array_equal(o["positions"], z["positions"])
+    assert np.array_equal(step_oracle.get_seq_lens(o["kv_block_indptrs"], o["kv_last_block_lens"], 16),
+                          z["seq_lens"])
+    assert (o["positions"] != o["position_ids"]).any()     # spare blocks: the two differ, as in flashinfer
+
+
 def hand_case():
     return [
         InferInput(input_ids=[7], input_len=1, filled_token_len=16, context_len=17, block_ids=[5, 9]),
