@@ -10,8 +10,10 @@ the oracle is pinned against LMServe's own Triton cache kernels
 (``runtime/worker/llm_worker/ops/triton/cache_kernels.py``) executed on CPU with
 the Triton interpreter; the outputs are committed under ``tests/golden/`` together
 with ``tests/golden/make_golden.py`` that produced them.  The swap and transfer
-restatements have no executable reference (pycuda / NIXL are not installable
-here) and follow ``kv_worker.py`` by reading: for those two, parity is unpinned.
+restatements are pinned the same way: LMServe's own ``kv_worker.py`` is loaded by path
+with stand-ins for pycuda / NIXL / the protobuf module (``oracle/kv_worker_ref.py``)
+and its methods are run on host buffers; ``tests/golden/make_swap_golden.py`` committed
+the vectors (``swap_*.npz``, ``transfer_*.npz``).
 ``rope_oracle`` has two arithmetic forms: rounded per operation (pinned for fp16 by the
 reference kernel under the Triton interpreter) and contracted as compiled Triton evaluates it
 (pinned for fp16 and bf16 by vectors made on a B200, ``tests/golden/rope_compiled_*.npz``).
