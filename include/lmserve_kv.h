@@ -59,8 +59,13 @@ typedef enum lms_status {
 /* Tunables for lms_set_tuning (a negative value restores the built-in choice; for the
  * non-variant keys 0 does too). */
 #define LMS_TUNE_WRITE_VARIANT 1 /* 0 = tiled 16-byte ld/st, 1 = tiled 32-byte, 2 = bulk-copy (TMA) rows,
-                                    3 = untiled one-vector-per-thread 32-byte, 4 = untiled 16-byte */
-#define LMS_TUNE_WRITE_TILE_BYTES 2 /* payload bytes read per CTA of the cache write */
+                                    3 = untiled one-vector-per-thread 32-byte, 4 = untiled 16-byte,
+                                    5 = one wave: a thread moves the K and the V vector of
+                                    LMS_TUNE_WRITE_VPT (1, 2, 4) tokens, 6 = one wave: a thread moves
+                                    LMS_TUNE_WRITE_VPT independent vectors, 7 = as 5 on a persistent
+                                    grid with a two-deep register pipeline */
+#define LMS_TUNE_WRITE_TILE_BYTES 2 /* payload bytes read per CTA of the tiled cache write; for variant 7
+                                       the CTAs per SM of the persistent grid */
 #define LMS_TUNE_COPY_VARIANT 3  /* 0 = persistent 16-byte ld/st, 1 = persistent 32-byte, 2 = bulk-copy (TMA),
                                     3 = untiled one-vector-per-thread, 4 = persistent 16-byte with
                                     1024-thread CTAs (128 KiB in flight per CTA, for grids of a few CTAs) */
@@ -210,6 +215,29 @@ int lms_append_paged_kv_cache(const void* key, const void* value,
                               const int32_t* kv_indptr, int64_t num_tokens,
                               int32_t num_layers, int64_t row_bytes,
                               int32_t block_size, int64_t num_blocks, void* stream);
+
+/*
+ * lms_append_paged_kv_cache with its arguments validated and resolved once: the per-layer
+ * call of runtime/worker/llm_worker/models/layers/attention.py:76-85 passes the same buffers
+ * every step (the index arrays are refilled in place), so the plan is built once per layer and
+ * lms_write_plan_run is then the whole per-call cost.  Run and destroy with
+ * lms_write_plan_run / lms_write_plan_destroy.  `num_requests` = entries of kv_indptr minus
+ * one (0 = not known): with it the kernel fetches kv_indptr[t] together with batch_indices[t]
+ * and positions[t] on the guess that token t belongs to request t - true for every token of a
+ * decode step - which leaves one dependent load (the page id) before the store instead of
+ * two; a wrong guess falls back to the plain walk, so the result never depends on it.
+ */
+int lms_paged_write_plan_create(const void* key, const void* value,
+                                int64_t key_token_stride, int64_t value_token_stride,
+                                int64_t key_layer_stride, int64_t value_layer_stride,
+                                const int32_t* batch_indices, const int32_t* positions,
+                                void* key_cache, void* value_cache,
+                                int64_t cache_layer_stride, int64_t block_stride,
+                                int64_t slot_stride, const int32_t* kv_indices,
+                                const int32_t* kv_indptr, int64_t num_requests,
+                                int64_t num_tokens, int32_t num_layers, int64_t row_bytes,
+                                int32_t block_size, int64_t num_blocks,
+                                lms_write_plan** plan);
 
 /*
  * Per-step index preparation on the device — replaces the host-side list building and the ten
@@ -393,6 +421,32 @@ int lms_swap_blocks_dma(int direction, void* gpu, int64_t gpu_layer_stride,
                         const int64_t* host_pairs, int64_t n_pairs,
                         int64_t num_gpu_blocks, int64_t num_host_blocks,
                         void* stream);
+/* The swap through a contiguous device staging buffer (replaces the per-(layer, block)
+ * cuMemcpy{HtoD,DtoH}Async loops of runtime/worker/llm_worker/kv_worker.py:206-211,222-227).
+ * Swap-out: a gather kernel packs the scattered (layer, block) chunks of a group of blocks
+ * into one half of `staging` ([block in group][layer][chunk], HBM to HBM), then the copy
+ * engines move every host block - or every run of host blocks with adjacent ids, after the
+ * pairs have been ordered by host block - in ONE transfer, on a copy stream owned by the
+ * library; the two halves alternate so that the transfer of one group overlaps the gather of
+ * the next.  Swap-in is the mirror image (large host-to-device transfers into a half, then a
+ * scatter kernel).  The SMs are busy for about 2 % of the swap; the link carries the copy
+ * engines' large packets instead of the 128-byte transactions SM-issued accesses become.
+ * `staging`: device memory of the caller, 256-byte aligned, `staging_bytes` >= twice the bytes
+ * of one block over the layer range (LMS_ERR_TOO_LARGE otherwise); two calls in the same
+ * direction that may overlap need a staging buffer each.  `host` is the address of the
+ * pinned pool; its layers of one block must be adjacent (host_layer_stride == chunk_bytes,
+ * else LMS_ERR_UNSUPPORTED).  Block ids are always range-checked on the host (when the
+ * bounds are > 0): the copy engines cannot skip a bad index, LMS_ERR_INDEX is returned
+ * before anything moves.  Work is complete when `stream` has passed the call.  Not for use
+ * inside stream capture.  Meant for whole-block swaps: with a one-layer range every
+ * transfer is one chunk and the rate drops to what single 64 KiB copies reach. */
+int lms_swap_blocks_staged(int direction, void* gpu, int64_t gpu_layer_stride,
+                           int64_t gpu_block_stride, void* host,
+                           int64_t host_block_stride, int64_t host_layer_stride,
+                           int64_t chunk_bytes, int32_t layer_begin, int32_t layer_end,
+                           const int64_t* host_pairs, int64_t n_pairs,
+                           int64_t num_gpu_blocks, int64_t num_host_blocks,
+                           void* staging, int64_t staging_bytes, void* stream);
 int lms_transfer_blocks_host(const void* src, int64_t src_layer_stride,
                              int64_t src_block_stride, void* dst,
                              int64_t dst_layer_stride, int64_t dst_block_stride,

@@ -67,6 +67,10 @@ SIGNATURES = {
         c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p,
         c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_int64,
         c_int32, c_int64, c_int32, c_int64, c_void_p]),
+    "lms_paged_write_plan_create": (c_int, [
+        c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p,
+        c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_int64, c_int64,
+        c_int32, c_int64, c_int32, c_int64, POINTER(c_void_p)]),
     "lms_rope_and_cache": (c_int, [
         c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int32, c_void_p,
         c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int64,
@@ -94,6 +98,9 @@ SIGNATURES = {
     "lms_swap_blocks_dma": (c_int, [
         c_int, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64,
         c_int32, c_int32, c_void_p, c_int64, c_int64, c_int64, c_void_p]),
+    "lms_swap_blocks_staged": (c_int, [
+        c_int, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64,
+        c_int32, c_int32, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_void_p]),
     "lms_transfer_blocks_host": (c_int, [
         c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64, c_int32,
         c_void_p, c_int64, c_int64, c_int64, c_void_p]),

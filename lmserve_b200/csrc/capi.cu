@@ -2,9 +2,11 @@
 // configuration, per-device state (SM count, error record) and the small
 // host-memory / IPC helpers.  Declarations and the reference call sites each
 // entry point replaces are in include/lmserve_kv.h.
+#include <algorithm>
 #include <atomic>
 #include <mutex>
 #include <new>
+#include <vector>
 #include <stdio.h>
 #include <string.h>
 
@@ -33,6 +35,16 @@ struct DeviceState {
   long long table_cap = 0;        // capacity in pairs
   cudaEvent_t table_free = nullptr;  // recorded after the kernel that last read `table`
   std::mutex table_mutex;
+  // Staged swap (lms_swap_blocks_staged), one set per direction: the copy-engine stream the
+  // large DMA transfers run on and the events that hand the two halves of the caller's
+  // staging buffer back and forth between that stream and the caller's stream.
+  struct Staged {
+    cudaStream_t copy = nullptr;
+    cudaEvent_t ready[2] = {nullptr, nullptr};  // half b holds data for the consumer
+    cudaEvent_t freed[2] = {nullptr, nullptr};  // half b has been consumed
+    cudaEvent_t start = nullptr;
+    std::mutex mutex;
+  } staged[2];
 };
 
 std::mutex g_mutex;
@@ -101,6 +113,7 @@ struct PagedIndex {
   const int32_t* positions = nullptr;
   const int32_t* page_indices = nullptr;
   const int32_t* page_indptr = nullptr;
+  int64_t num_requests = 0;  // entries of page_indptr minus one; 0 = not known
 };
 
 // Validates the arguments of a write and fills the kernel parameter block (everything but
@@ -150,6 +163,8 @@ int write_params(const void* key, const void* value, int64_t key_tok,
     p.positions = paged->positions;
     p.page_indices = paged->page_indices;
     p.page_indptr = paged->page_indptr;
+    if (paged->num_requests < 0 || paged->num_requests > 0x7fffffffll) return LMS_ERR_RANGE;
+    p.num_requests = (int)paged->num_requests;
   }
   p.key_tok = key_tok;
   p.val_tok = val_tok;
@@ -363,7 +378,7 @@ int lms_set_tuning(int key, int value) {
   const bool is_variant = key == LMS_TUNE_WRITE_VARIANT || key == LMS_TUNE_COPY_VARIANT ||
                           key == LMS_TUNE_XFER_VARIANT || key == LMS_TUNE_SWAP_VARIANT;
   if (is_variant) {
-    if (value > 4) return LMS_ERR_RANGE;
+    if (value > (key == LMS_TUNE_WRITE_VARIANT ? 7 : 4)) return LMS_ERR_RANGE;
     g_tuning[key].store(value < 0 ? 0 : value + 1);
   } else {
     g_tuning[key].store(value < 0 ? 0 : value);
@@ -510,6 +525,44 @@ int lms_append_paged_kv_cache(const void* key, const void* value,
                       cache_layer_stride, block_stride, slot_stride, nullptr, 0,
                       num_tokens, num_layers, row_bytes, block_size,
                       num_blocks * (int64_t)block_size, stream, &paged);
+}
+
+int lms_paged_write_plan_create(const void* key, const void* value,
+                                int64_t key_token_stride, int64_t value_token_stride,
+                                int64_t key_layer_stride, int64_t value_layer_stride,
+                                const int32_t* batch_indices, const int32_t* positions,
+                                void* key_cache, void* value_cache,
+                                int64_t cache_layer_stride, int64_t block_stride,
+                                int64_t slot_stride, const int32_t* kv_indices,
+                                const int32_t* kv_indptr, int64_t num_requests,
+                                int64_t num_tokens, int32_t num_layers, int64_t row_bytes,
+                                int32_t block_size, int64_t num_blocks,
+                                lms_write_plan** plan) {
+  if (!plan) return LMS_ERR_NULL;
+  *plan = nullptr;
+  if (num_blocks < 0 || num_blocks > (1ll << 40)) return LMS_ERR_RANGE;
+  PagedIndex paged;
+  paged.batch_idx = batch_indices;
+  paged.positions = positions;
+  paged.page_indices = kv_indices;
+  paged.page_indptr = kv_indptr;
+  paged.num_requests = num_requests;
+  WriteParams p{};
+  bool empty = false;
+  if (int rc = write_params(key, value, key_token_stride, value_token_stride,
+                            key_layer_stride, value_layer_stride, key_cache, value_cache,
+                            cache_layer_stride, block_stride, slot_stride, nullptr, 0,
+                            num_tokens, num_layers, row_bytes, block_size,
+                            num_blocks * (int64_t)block_size, &paged, &p, &empty))
+    return rc;
+  DeviceState* ds = nullptr;
+  if (int rc = device_state(&ds)) return rc;
+  lms_write_plan* out = new (std::nothrow) lms_write_plan;
+  if (!out) return LMS_ERR_UNSUPPORTED;
+  out->params = p;
+  out->empty = empty;
+  *plan = out;
+  return LMS_OK;
 }
 
 int lms_rope_and_cache(const void* query, const void* key, const void* value,
@@ -819,6 +872,145 @@ int swap_blocks_dma(int direction, char* gpu, int64_t gpu_layer_stride,
   return LMS_OK;
 }
 
+// Swap through a contiguous device staging ring: the SMs only move HBM -> HBM (gather the
+// scattered chunks of a group of blocks into one half of the staging buffer, or scatter them
+// out of it) and the PCIe hop is done by the copy engines in transfers of whole host blocks -
+// or of runs of adjacent host blocks - which use the link's large packets.  The two halves
+// alternate, so the DMA of one group overlaps the gather / scatter of the next.
+int staged_setup(DeviceState::Staged& st) {
+  if (st.copy != nullptr) return LMS_OK;
+  LMS_CUDA(cudaStreamCreateWithFlags(&st.copy, cudaStreamNonBlocking));
+  for (int b = 0; b < 2; ++b) {
+    LMS_CUDA(cudaEventCreateWithFlags(&st.ready[b], cudaEventDisableTiming));
+    LMS_CUDA(cudaEventCreateWithFlags(&st.freed[b], cudaEventDisableTiming));
+  }
+  LMS_CUDA(cudaEventCreateWithFlags(&st.start, cudaEventDisableTiming));
+  return LMS_OK;
+}
+
+int swap_blocks_staged(int direction, char* gpu, int64_t gpu_layer_stride,
+                       int64_t gpu_block_stride, char* host, int64_t host_block_stride,
+                       int64_t host_layer_stride, int64_t chunk_bytes, int32_t layer_begin,
+                       int32_t layer_end, const int64_t* pairs, int64_t n_pairs,
+                       int64_t num_gpu_blocks, int64_t num_host_blocks, char* staging,
+                       int64_t staging_bytes, cudaStream_t stream) {
+  if (direction != LMS_SWAP_OUT && direction != LMS_SWAP_IN) return LMS_ERR_RANGE;
+  if (layer_begin < 0 || layer_end < layer_begin || n_pairs < 0 || chunk_bytes <= 0 ||
+      chunk_bytes > (1ll << 30) || staging_bytes < 0)
+    return LMS_ERR_RANGE;
+  const int nl = layer_end - layer_begin;
+  if (n_pairs == 0 || nl == 0) return LMS_OK;
+  if (!gpu || !host || !pairs || !staging) return LMS_ERR_NULL;
+  if (!mult16(gpu_layer_stride) || !mult16(gpu_block_stride) || !mult16(host_block_stride) ||
+      !mult16(host_layer_stride) || !mult16(chunk_bytes) || !ptr16(gpu) || !ptr16(host) ||
+      ((uintptr_t)staging & 255u) != 0)
+    return LMS_ERR_ALIGN;
+  // The layers of one host block must be adjacent, or a block is not one DMA transfer.
+  if (host_layer_stride != chunk_bytes) return LMS_ERR_UNSUPPORTED;
+  const bool out = direction == LMS_SWAP_OUT;
+  const int64_t per_block = (int64_t)nl * chunk_bytes;
+  const int64_t half = (staging_bytes / 2) & ~(int64_t)255;
+  const int64_t group = half / per_block;  // blocks per half
+  if (group < 1) return LMS_ERR_TOO_LARGE;
+
+  // (host block, gpu block), ordered by host block so that adjacent host blocks form runs.
+  std::vector<std::pair<int64_t, int64_t>> order((size_t)n_pairs);
+  for (int64_t i = 0; i < n_pairs; ++i) {
+    const int64_t g = out ? pairs[2 * i] : pairs[2 * i + 1];
+    const int64_t h = out ? pairs[2 * i + 1] : pairs[2 * i];
+    if (g < 0 || h < 0 || (num_gpu_blocks > 0 && g >= num_gpu_blocks) ||
+        (num_host_blocks > 0 && h >= num_host_blocks)) {
+      // unlike the kernels, the copy engines cannot skip a bad index: it is always refused
+      snprintf(g_cuda_msg, sizeof(g_cuda_msg), "block pair %lld (%lld, %lld) is out of range",
+               (long long)i, (long long)pairs[2 * i], (long long)pairs[2 * i + 1]);
+      return LMS_ERR_INDEX;
+    }
+    order[(size_t)i] = {h, g};
+  }
+  std::sort(order.begin(), order.end());
+  // Kernel table: (gpu block, position inside its group's half of the staging buffer).
+  std::vector<int64_t> table((size_t)n_pairs * 2);
+  for (int64_t i = 0; i < n_pairs; ++i) {
+    table[(size_t)(2 * i + (out ? 0 : 1))] = order[(size_t)i].second;
+    table[(size_t)(2 * i + (out ? 1 : 0))] = i % group;
+  }
+
+  DeviceState* ds = nullptr;
+  if (int rc = device_state(&ds)) return rc;
+  DeviceState::Staged& st = ds->staged[out ? 0 : 1];
+  std::lock_guard<std::mutex> lock(st.mutex);
+  if (int rc = staged_setup(st)) return rc;
+  // A whole run of adjacent host blocks is one transfer only if consecutive blocks touch.
+  const bool runs = host_block_stride == per_block;
+  char* gbase = gpu + (long long)layer_begin * gpu_layer_stride;
+  char* hbase = host + (long long)layer_begin * host_layer_stride;
+  const int64_t n_groups = (n_pairs + group - 1) / group;
+  const int ctas = ds->sms * 2;
+
+  return with_host_table(table.data(), n_pairs, stream, [&](const int64_t* dev_table) {
+    if (!out) {
+      // the DMA reads host memory that earlier work of the caller's stream may still write
+      LMS_CUDA(cudaEventRecord(st.start, stream));
+      LMS_CUDA(cudaStreamWaitEvent(st.copy, st.start, 0));
+    }
+    for (int64_t g = 0; g < n_groups; ++g) {
+      const int b = (int)(g & 1);
+      const int64_t first = g * group;
+      const int64_t count = std::min(group, n_pairs - first);
+      char* buf = staging + (int64_t)b * half;
+      auto dma = [&]() -> int {
+        for (int64_t k = 0; k < count;) {
+          int64_t len = 1;
+          if (runs)
+            while (k + len < count &&
+                   order[(size_t)(first + k + len)].first == order[(size_t)(first + k)].first + len)
+              ++len;
+          char* h = hbase + order[(size_t)(first + k)].first * host_block_stride;
+          char* d = buf + k * per_block;
+          if (out)
+            LMS_CUDA(cudaMemcpyAsync(h, d, (size_t)(len * per_block), cudaMemcpyDeviceToHost, st.copy));
+          else
+            LMS_CUDA(cudaMemcpyAsync(d, h, (size_t)(len * per_block), cudaMemcpyHostToDevice, st.copy));
+          k += len;
+        }
+        return LMS_OK;
+      };
+      auto kernel = [&]() -> int {
+        if (out)
+          return chunk_copy(gbase, gpu_layer_stride, gpu_block_stride, buf, chunk_bytes,
+                            per_block, chunk_bytes, nl, dev_table + 2 * first, count,
+                            num_gpu_blocks, group, /*layer_major=*/0, kWhereSwapOut,
+                            tuned_variant(LMS_TUNE_COPY_VARIANT, 3), 0, ctas, stream);
+        return chunk_copy(buf, chunk_bytes, per_block, gbase, gpu_layer_stride,
+                          gpu_block_stride, chunk_bytes, nl, dev_table + 2 * first, count, group,
+                          num_gpu_blocks, /*layer_major=*/0, kWhereSwapIn,
+                          tuned_variant(LMS_TUNE_COPY_VARIANT, 3), 0, ctas, stream);
+      };
+      if (out) {
+        if (g >= 2) LMS_CUDA(cudaStreamWaitEvent(stream, st.freed[b], 0));
+        if (int rc = kernel()) return rc;
+        LMS_CUDA(cudaEventRecord(st.ready[b], stream));
+        LMS_CUDA(cudaStreamWaitEvent(st.copy, st.ready[b], 0));
+        if (int rc = dma()) return rc;
+        LMS_CUDA(cudaEventRecord(st.freed[b], st.copy));
+      } else {
+        if (g >= 2) LMS_CUDA(cudaStreamWaitEvent(st.copy, st.freed[b], 0));
+        if (int rc = dma()) return rc;
+        LMS_CUDA(cudaEventRecord(st.ready[b], st.copy));
+        LMS_CUDA(cudaStreamWaitEvent(stream, st.ready[b], 0));
+        if (int rc = kernel()) return rc;
+        LMS_CUDA(cudaEventRecord(st.freed[b], stream));
+      }
+    }
+    if (out) {
+      // the caller's stream completes when the last transfers have landed in host memory
+      LMS_CUDA(cudaStreamWaitEvent(stream, st.freed[(n_groups - 1) & 1], 0));
+      if (n_groups >= 2) LMS_CUDA(cudaStreamWaitEvent(stream, st.freed[n_groups & 1], 0));
+    }
+    return (int)LMS_OK;
+  });
+}
+
 }  // namespace
 
 extern "C" {
@@ -835,6 +1027,20 @@ int lms_swap_blocks_dma(int direction, void* gpu, int64_t gpu_layer_stride,
                          (char*)host, host_block_stride, host_layer_stride, chunk_bytes,
                          layer_begin, layer_end, host_pairs, n_pairs, num_gpu_blocks,
                          num_host_blocks, (cudaStream_t)stream);
+}
+
+int lms_swap_blocks_staged(int direction, void* gpu, int64_t gpu_layer_stride,
+                           int64_t gpu_block_stride, void* host,
+                           int64_t host_block_stride, int64_t host_layer_stride,
+                           int64_t chunk_bytes, int32_t layer_begin, int32_t layer_end,
+                           const int64_t* host_pairs, int64_t n_pairs,
+                           int64_t num_gpu_blocks, int64_t num_host_blocks,
+                           void* staging, int64_t staging_bytes, void* stream) {
+  return swap_blocks_staged(direction, (char*)gpu, gpu_layer_stride, gpu_block_stride,
+                            (char*)host, host_block_stride, host_layer_stride, chunk_bytes,
+                            layer_begin, layer_end, host_pairs, n_pairs, num_gpu_blocks,
+                            num_host_blocks, (char*)staging, staging_bytes,
+                            (cudaStream_t)stream);
 }
 
 int lms_swap_blocks_host(int direction, void* gpu, int64_t gpu_layer_stride,

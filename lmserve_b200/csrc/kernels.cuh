@@ -36,6 +36,7 @@ struct WriteParams {
   const int* positions;
   const int* page_indices;
   const int* page_indptr;
+  int num_requests;                // paged: entries of page_indptr minus one, 0 = not known
   long long key_tok, val_tok;      // bytes between consecutive tokens
   long long key_layer, val_layer;  // bytes between consecutive layers (inputs)
   long long cache_layer;           // bytes between consecutive layers (cache)

@@ -67,19 +67,27 @@ __device__ __forceinline__ void split_vec(int v, int row_vecs, int row_shift,
 struct SlotRaw {
   long long a;  // direct: the slot;  paged: batch index
   int b;        // paged: position
+  int ip;       // paged: page_indptr[min(t, num_requests)], read on the guess batch_idx[t] == t
 };
 __device__ __forceinline__ SlotRaw slot_fetch_begin(const WriteParams& p, int layer, int t) {
   SlotRaw r;
   r.b = 0;
+  r.ip = 0;
   if (p.slots != nullptr) {
     r.a = p.slots[(long long)layer * p.slot_layer + t];
   } else {
     r.a = p.batch_idx[t];
     r.b = p.positions[t];
+    // A decode step appends one token per request, so token t belongs to request t.  When the
+    // caller said how many requests the page table has, the request's page-table offset is
+    // fetched on that guess together with the two loads above; a right guess leaves one
+    // dependent load (the page id) where the plain walk has two.
+    if (p.num_requests > 0) r.ip = p.page_indptr[t < p.num_requests ? t : p.num_requests];
   }
   return r;
 }
-__device__ __forceinline__ long long slot_fetch_end(const WriteParams& p, const SlotRaw& r) {
+__device__ __forceinline__ long long slot_fetch_end(const WriteParams& p, const SlotRaw& r,
+                                                    int t) {
   if (p.slots != nullptr) return r.a;
   if (r.a < 0 || r.b < 0) return -1;  // padding: negative batch index or position
   int pg, in;
@@ -90,7 +98,8 @@ __device__ __forceinline__ long long slot_fetch_end(const WriteParams& p, const 
     pg = r.b / p.block_size;
     in = r.b - pg * p.block_size;
   }
-  const long long page = p.page_indices[p.page_indptr[r.a] + pg];
+  const int first = (p.num_requests > 0 && r.a == t) ? r.ip : p.page_indptr[r.a];
+  const long long page = p.page_indices[first + pg];
   return page * p.block_size + in;
 }
 
@@ -157,7 +166,7 @@ write_rows_vec(const WriteParams p, const int row_vecs, const int row_shift) {
   for (int k = 0; k < kSlotsPerThread; ++k) {
     const int i = k * THREADS + threadIdx.x;
     if (i < nt)
-      s_off[i] = slot_offset(p, slot_fetch_end(p, my_slot[k]),
+      s_off[i] = slot_offset(p, slot_fetch_end(p, my_slot[k], t0 + i),
                              (long long)layer * p.slot_layer + t0 + i);
   }
   __syncthreads();
@@ -186,11 +195,9 @@ write_rows_direct(const WriteParams p, const int row_vecs, const int row_shift,
   // Nothing is read or written before that kernel has completed and its writes are visible,
   // so stream order is exactly what it would be without the attribute; only the launch
   // latency is hidden.  The kernel that follows this one is allowed to do the same.
-  asm volatile("griddepcontrol.wait;" ::: "memory");
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const long long v = (long long)blockIdx.x * THREADS + threadIdx.x;
-  if (v >= n_vec_total) return;
-  // v = ((layer * T + t) * 2 + kv) * row_vecs + c
+  // v = ((layer * T + t) * 2 + kv) * row_vecs + c; the arithmetic needs no memory, so it is
+  // done before the wait
   long long q;
   int c;
   if (POW2) {
@@ -202,8 +209,17 @@ write_rows_direct(const WriteParams p, const int row_vecs, const int row_shift,
   }
   const int kv = (int)(q & 1);
   q >>= 1;
-  const int layer = (int)(q / p.num_tokens);
-  const int t = (int)(q - (long long)layer * p.num_tokens);
+  int layer, t;
+  if (n_vec_total <= 0x7fffffffll) {  // 32-bit division where the launch allows it
+    layer = (int)((unsigned)q / (unsigned)p.num_tokens);
+    t = (int)((unsigned)q - (unsigned)layer * (unsigned)p.num_tokens);
+  } else {
+    layer = (int)(q / p.num_tokens);
+    t = (int)(q - (long long)layer * p.num_tokens);
+  }
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (v >= n_vec_total) return;
 
   const SlotRaw raw = slot_fetch_begin(p, layer, t);
   const char* src = (kv ? p.value + (long long)layer * p.val_layer + (long long)t * p.val_tok
@@ -212,11 +228,205 @@ write_rows_direct(const WriteParams p, const int row_vecs, const int row_shift,
   Vec r;
   ld(r, src);
   const long long off =
-      slot_offset(p, slot_fetch_end(p, raw), (long long)layer * p.slot_layer + t);
+      slot_offset(p, slot_fetch_end(p, raw, t), (long long)layer * p.slot_layer + t);
   if (off >= 0)
     st((kv ? p.vcache : p.kcache) + (long long)layer * p.cache_layer + off +
            (long long)c * Vec::kBytes,
        r);
+}
+
+// A decode step in at most one wave.  Unit u of a layer is (token t, vector c of the row): the
+// thread that owns it moves vector c of the K row AND of the V row of token t, so one slot
+// resolution serves two payload vectors, and a thread owns TOK units THREADS apart (the
+// accesses of a warp stay contiguous).  The layer is blockIdx.y, which removes the division by
+// the token count; all index arithmetic is done before the programmatic-launch wait, all
+// 2 * TOK payload loads and the TOK index loads are in flight together, then the stores.
+// With TOK = 2 the 40 MiB step of a 70B TP8 shard is 640 CTAs (0.54 of a wave at 8 CTAs per
+// SM), so the whole grid is resident - and waiting in griddepcontrol.wait - before the
+// previous kernel of the stream has finished.
+template <class Vec, int THREADS, int TOK, bool POW2>
+__global__ void __launch_bounds__(THREADS)
+write_rows_pair(const WriteParams p, const int row_vecs, const int row_shift,
+                const int units_per_layer) {
+  const int layer = blockIdx.y;
+  const int base = blockIdx.x * (THREADS * TOK) + threadIdx.x;
+  int t[TOK], c[TOK];
+#pragma unroll
+  for (int j = 0; j < TOK; ++j) {
+    const int u = base + j * THREADS;
+    if (POW2) {
+      c[j] = u & (row_vecs - 1);
+      t[j] = u >> row_shift;
+    } else {
+      t[j] = u / row_vecs;
+      c[j] = u - t[j] * row_vecs;
+    }
+    if (u >= units_per_layer) t[j] = -1;
+  }
+  const char* kin = p.key + (long long)layer * p.key_layer;
+  const char* vin = p.value + (long long)layer * p.val_layer;
+  char* kout = p.kcache + (long long)layer * p.cache_layer;
+  char* vout = p.vcache + (long long)layer * p.cache_layer;
+
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+  SlotRaw raw[TOK];
+  Vec rk[TOK], rv[TOK];
+#pragma unroll
+  for (int j = 0; j < TOK; ++j)
+    if (t[j] >= 0) raw[j] = slot_fetch_begin(p, layer, t[j]);
+#pragma unroll
+  for (int j = 0; j < TOK; ++j)
+    if (t[j] >= 0) {
+      ld(rk[j], kin + (long long)t[j] * p.key_tok + (long long)c[j] * Vec::kBytes);
+      ld(rv[j], vin + (long long)t[j] * p.val_tok + (long long)c[j] * Vec::kBytes);
+    }
+#pragma unroll
+  for (int j = 0; j < TOK; ++j)
+    if (t[j] >= 0) {
+      const long long off = slot_offset(p, slot_fetch_end(p, raw[j], t[j]),
+                                        (long long)layer * p.slot_layer + t[j]);
+      if (off >= 0) {
+        st(kout + off + (long long)c[j] * Vec::kBytes, rk[j]);
+        st(vout + off + (long long)c[j] * Vec::kBytes, rv[j]);
+      }
+    }
+}
+
+// The same units walked by a persistent grid (at most one wave) with a two-deep register
+// pipeline: the loads of the CTA's next tile are in flight while the current tile is stored.
+// A tile is THREADS * TOK units of one layer; tiles are numbered layer by layer.
+template <class Vec, int THREADS, int TOK, bool POW2>
+__global__ void __launch_bounds__(THREADS)
+write_rows_pair_persistent(const WriteParams p, const int row_vecs, const int row_shift,
+                           const int units_per_layer, const int tiles_per_layer,
+                           const int n_tiles) {
+  struct Tile {
+    int layer;
+    int t[TOK], c[TOK];
+    SlotRaw raw[TOK];
+    Vec rk[TOK], rv[TOK];
+  };
+  auto locate = [&](Tile& x, int tile) {
+    x.layer = tile / tiles_per_layer;
+    const int base = (tile - x.layer * tiles_per_layer) * (THREADS * TOK) + threadIdx.x;
+#pragma unroll
+    for (int j = 0; j < TOK; ++j) {
+      const int u = base + j * THREADS;
+      if (POW2) {
+        x.c[j] = u & (row_vecs - 1);
+        x.t[j] = u >> row_shift;
+      } else {
+        x.t[j] = u / row_vecs;
+        x.c[j] = u - x.t[j] * row_vecs;
+      }
+      if (u >= units_per_layer) x.t[j] = -1;
+    }
+  };
+  auto load = [&](Tile& x) {
+    const char* kin = p.key + (long long)x.layer * p.key_layer;
+    const char* vin = p.value + (long long)x.layer * p.val_layer;
+#pragma unroll
+    for (int j = 0; j < TOK; ++j)
+      if (x.t[j] >= 0) x.raw[j] = slot_fetch_begin(p, x.layer, x.t[j]);
+#pragma unroll
+    for (int j = 0; j < TOK; ++j)
+      if (x.t[j] >= 0) {
+        ld(x.rk[j], kin + (long long)x.t[j] * p.key_tok + (long long)x.c[j] * Vec::kBytes);
+        ld(x.rv[j], vin + (long long)x.t[j] * p.val_tok + (long long)x.c[j] * Vec::kBytes);
+      }
+  };
+  auto store = [&](const Tile& x) {
+    char* kout = p.kcache + (long long)x.layer * p.cache_layer;
+    char* vout = p.vcache + (long long)x.layer * p.cache_layer;
+#pragma unroll
+    for (int j = 0; j < TOK; ++j)
+      if (x.t[j] >= 0) {
+        const long long off = slot_offset(p, slot_fetch_end(p, x.raw[j], x.t[j]),
+                                          (long long)x.layer * p.slot_layer + x.t[j]);
+        if (off >= 0) {
+          st(kout + off + (long long)x.c[j] * Vec::kBytes, x.rk[j]);
+          st(vout + off + (long long)x.c[j] * Vec::kBytes, x.rv[j]);
+        }
+      }
+  };
+
+  Tile a, b;
+  int tile = blockIdx.x;
+  if (tile < n_tiles) locate(a, tile);
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (tile >= n_tiles) return;
+  load(a);
+  for (;;) {
+    int next = tile + gridDim.x;
+    if (next < n_tiles) {
+      locate(b, next);
+      load(b);
+    }
+    store(a);
+    if (next >= n_tiles) break;
+    tile = next;
+    next = tile + gridDim.x;
+    if (next < n_tiles) {
+      locate(a, next);
+      load(a);
+    }
+    store(b);
+    if (next >= n_tiles) break;
+    tile = next;
+  }
+}
+
+// VPT independent vectors per thread of the flattened (token, K|V, vector) space of one layer
+// (blockIdx.y); every vector resolves its own slot.
+template <class Vec, int THREADS, int VPT, bool POW2>
+__global__ void __launch_bounds__(THREADS)
+write_rows_multi(const WriteParams p, const int row_vecs, const int row_shift,
+                 const int vecs_per_layer) {
+  const int layer = blockIdx.y;
+  const int base = blockIdx.x * (THREADS * VPT) + threadIdx.x;
+  int t[VPT], c[VPT], kv[VPT];
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    const int v = base + j * THREADS;
+    int q;
+    if (POW2) {
+      c[j] = v & (row_vecs - 1);
+      q = v >> row_shift;
+    } else {
+      q = v / row_vecs;
+      c[j] = v - q * row_vecs;
+    }
+    kv[j] = q & 1;
+    t[j] = v < vecs_per_layer ? (q >> 1) : -1;
+  }
+  const char* kin = p.key + (long long)layer * p.key_layer;
+  const char* vin = p.value + (long long)layer * p.val_layer;
+  char* kout = p.kcache + (long long)layer * p.cache_layer;
+  char* vout = p.vcache + (long long)layer * p.cache_layer;
+
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+  SlotRaw raw[VPT];
+  Vec r[VPT];
+#pragma unroll
+  for (int j = 0; j < VPT; ++j)
+    if (t[j] >= 0) raw[j] = slot_fetch_begin(p, layer, t[j]);
+#pragma unroll
+  for (int j = 0; j < VPT; ++j)
+    if (t[j] >= 0)
+      ld(r[j], (kv[j] ? vin + (long long)t[j] * p.val_tok : kin + (long long)t[j] * p.key_tok) +
+                   (long long)c[j] * Vec::kBytes);
+#pragma unroll
+  for (int j = 0; j < VPT; ++j)
+    if (t[j] >= 0) {
+      const long long off = slot_offset(p, slot_fetch_end(p, raw[j], t[j]),
+                                        (long long)layer * p.slot_layer + t[j]);
+      if (off >= 0) st((kv[j] ? vout : kout) + off + (long long)c[j] * Vec::kBytes, r[j]);
+    }
 }
 
 // One piece per lane per iteration; a warp-task is 32 consecutive pieces of
@@ -257,7 +467,7 @@ write_rows_bulk(const WriteParams p, const long long n_items) {
       const int layer = (int)(q / p.num_tokens);
       const long long si = (long long)layer * p.slot_layer + t;
       const long long off =
-          slot_offset(p, slot_fetch_end(p, slot_fetch_begin(p, layer, t)), si);
+          slot_offset(p, slot_fetch_end(p, slot_fetch_begin(p, layer, t), t), si);
       if (off >= 0) {
         const long long po = (long long)piece * p.piece_bytes;
         src = (kv ? p.value + (long long)layer * p.val_layer + (long long)t * p.val_tok
@@ -357,6 +567,70 @@ cudaError_t launch_direct(const WriteParams& p, bool pdl, cudaStream_t stream) {
                             row_shift, n_vec);
 }
 
+// Launch attributes shared by the untiled kernels.
+struct PdlConfig {
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  PdlConfig(dim3 grid, int threads, bool pdl, cudaStream_t stream) {
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(threads);
+    cfg.stream = stream;
+    if (pdl) {
+      attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[0].val.programmaticStreamSerializationAllowed = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+    }
+  }
+};
+
+// kind 5: (K, V) vector pairs, TOK units per thread, one CTA tile per THREADS * TOK units;
+// kind 7: the same tiles walked by a persistent grid of `sms * ctas_per_sm` CTAs;
+// kind 6: VPT independent vectors per thread.
+template <class Vec, int N>
+cudaError_t launch_wave(const WriteParams& p, int kind, bool pdl, int sms, int ctas_per_sm,
+                        cudaStream_t stream) {
+  constexpr int THREADS = 256;
+  const int row_vecs = p.row_bytes / Vec::kBytes;
+  const int row_shift = ilog2_exact(row_vecs);
+  const long long per_layer = (long long)p.num_tokens * row_vecs * (kind == 6 ? 2 : 1);
+  if (per_layer > 0x3fffffffll || p.num_layers > 65535) return cudaErrorInvalidConfiguration;
+  const int tiles = (int)((per_layer + THREADS * N - 1) / (THREADS * N));
+  if (kind == 7) {
+    const long long n_tiles = (long long)tiles * p.num_layers;
+    if (n_tiles > 0x7fffffffll) return cudaErrorInvalidConfiguration;
+    long long grid = (long long)sms * (ctas_per_sm > 0 ? ctas_per_sm : 4);
+    if (grid > n_tiles) grid = n_tiles;
+    PdlConfig c(dim3((unsigned)grid), THREADS, pdl, stream);
+    if (row_shift >= 0)
+      return cudaLaunchKernelEx(&c.cfg, write_rows_pair_persistent<Vec, THREADS, N, true>, p,
+                                row_vecs, row_shift, (int)per_layer, tiles, (int)n_tiles);
+    return cudaLaunchKernelEx(&c.cfg, write_rows_pair_persistent<Vec, THREADS, N, false>, p,
+                              row_vecs, row_shift, (int)per_layer, tiles, (int)n_tiles);
+  }
+  PdlConfig c(dim3((unsigned)tiles, (unsigned)p.num_layers), THREADS, pdl, stream);
+  if (kind == 6) {
+    if (row_shift >= 0)
+      return cudaLaunchKernelEx(&c.cfg, write_rows_multi<Vec, THREADS, N, true>, p, row_vecs,
+                                row_shift, (int)per_layer);
+    return cudaLaunchKernelEx(&c.cfg, write_rows_multi<Vec, THREADS, N, false>, p, row_vecs,
+                              row_shift, (int)per_layer);
+  }
+  if (row_shift >= 0)
+    return cudaLaunchKernelEx(&c.cfg, write_rows_pair<Vec, THREADS, N, true>, p, row_vecs,
+                              row_shift, (int)per_layer);
+  return cudaLaunchKernelEx(&c.cfg, write_rows_pair<Vec, THREADS, N, false>, p, row_vecs,
+                            row_shift, (int)per_layer);
+}
+
+template <class Vec>
+cudaError_t launch_wave_n(const WriteParams& p, int kind, int n, bool pdl, int sms,
+                          int ctas_per_sm, cudaStream_t stream) {
+  if (n >= 4) return launch_wave<Vec, 4>(p, kind, pdl, sms, ctas_per_sm, stream);
+  if (n >= 2) return launch_wave<Vec, 2>(p, kind, pdl, sms, ctas_per_sm, stream);
+  return launch_wave<Vec, 1>(p, kind, pdl, sms, ctas_per_sm, stream);
+}
+
 template <class Vec>
 cudaError_t launch_vec_vpt(const WriteParams& p, int tile_bytes, int vpt, int sms,
                            cudaStream_t stream) {
@@ -394,6 +668,11 @@ cudaError_t launch_write(const WriteParams& p_in, int variant, int tile_bytes,
   if (variant == 3)
     return a32 ? launch_direct<V32>(p, pdl, stream) : launch_direct<V16>(p, pdl, stream);
   if (variant == 4) return launch_direct<V16>(p, pdl, stream);
+  if (variant >= 5 && variant <= 7) {
+    // tile_bytes doubles as "CTAs per SM" of the persistent form
+    return a32 ? launch_wave_n<V32>(p, variant, vpt, pdl, sms, tile_bytes, stream)
+               : launch_wave_n<V16>(p, variant, vpt, pdl, sms, tile_bytes, stream);
+  }
 
   if (variant == 2) {
     // piece = the largest power-of-two divisor of the row, capped at 1 KiB

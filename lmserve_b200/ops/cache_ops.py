@@ -225,32 +225,12 @@ def reshape_and_cache_layers(
     _write_layers(key, value, kv_caches, slot_mapping)
 
 
-def append_paged_kv_cache(
-    append_key: torch.Tensor,
-    append_value: torch.Tensor,
-    batch_indices: torch.Tensor,
-    positions: torch.Tensor,
-    paged_kv_cache,
-    kv_indices: torch.Tensor,
-    kv_indptr: torch.Tensor,
-    kv_last_page_len: Optional[torch.Tensor] = None,
-    kv_layout: str = "NHD",
-) -> None:
-    """Drop-in for ``flashinfer.append_paged_kv_cache`` as LMServe calls it
-    (``models/layers/attention.py:76-85``): same argument order and meaning, same in-place
-    result, so the call site changes only its import.
-
-    ``append_key``/``append_value``: ``[T, H, D]``; ``batch_indices``/``positions``: int32
-    ``[T]`` (request index and position of every appended token, as produced by
-    ``flashinfer.get_batch_indices_positions`` at ``model_worker.py:425-433``);
-    ``paged_kv_cache``: one layer's ``[num_pages, 2, page_size, H, D]`` tensor, or a
-    ``(k_cache, v_cache)`` pair of ``[num_pages, page_size, H, D]`` tensors; ``kv_indices`` /
-    ``kv_indptr``: int32 page table in CSR form.  ``kv_last_page_len`` is accepted and ignored
-    (the write does not need it).  Only the ``"NHD"`` layout, the one LMServe uses.
-    """
+def _prepare_paged(append_key, append_value, batch_indices, positions, paged_kv_cache,
+                   kv_indices, kv_indptr, kv_layout):
+    """Validates a paged append and returns (device, argument tuple of
+    ``lms_paged_write_plan_create`` without the plan pointer).  Attribute reads only."""
     if kv_layout != "NHD":
         raise ValueError("only the NHD layout (LMServe's) is supported")
-    # This runs once per layer per step: checks are kept to attribute reads.
     if type(paged_kv_cache) is torch.Tensor:
         cache = paged_kv_cache
         cshape = cache.shape
@@ -304,17 +284,116 @@ def append_paged_kv_cache(
             raise ValueError(f"{name} must be a contiguous tensor on the cache's device")
     if batch_indices.numel() != T or positions.numel() != T:
         raise ValueError("batch_indices and positions need one entry per appended token")
-    if T == 0:
-        return
     row_bytes = H * D * es
-    with _OnDevice(dev):
-        rc = _lib.lib().lms_append_paged_kv_cache(
-            append_key.data_ptr(), append_value.data_ptr(), ks[0] * es, vs[0] * es, 0, 0,
-            batch_indices.data_ptr(), positions.data_ptr(), kptr, vptr, 0, block_stride,
-            row_bytes, kv_indices.data_ptr(), kv_indptr.data_ptr(), T, 1, row_bytes, BS, NB,
-            _stream_ptr(dev))
-    if rc:
-        _lib.check(rc)
+    num_requests = max(0, kv_indptr.numel() - 1)
+    return dev, (append_key.data_ptr(), append_value.data_ptr(), ks[0] * es, vs[0] * es, 0, 0,
+                 batch_indices.data_ptr(), positions.data_ptr(), kptr, vptr, 0, block_stride,
+                 row_bytes, kv_indices.data_ptr(), kv_indptr.data_ptr(), num_requests, T, 1,
+                 row_bytes, BS, NB)
+
+
+class PagedWritePlan:
+    """A paged append (``flashinfer.append_paged_kv_cache``'s arguments) validated and resolved
+    once; ``run()`` is one C call.  LMServe's attention layer passes the same buffers every
+    step (``models/layers/attention.py:76-85`` with the step tensors of
+    ``model_worker.py:399-433``), so one plan per layer serves the whole decode loop.  The plan
+    records addresses and geometry, not tensors: it must be rebuilt when a tensor is
+    reallocated (``append_paged_kv_cache`` does that by itself)."""
+
+    __slots__ = ("device", "_handle", "_run", "_destroy", "_index")
+
+    def __init__(self, append_key, append_value, batch_indices, positions, paged_kv_cache,
+                 kv_indices, kv_indptr, kv_last_page_len=None, kv_layout: str = "NHD"):
+        self.device, args = _prepare_paged(append_key, append_value, batch_indices, positions,
+                                           paged_kv_cache, kv_indices, kv_indptr, kv_layout)
+        self._index = self.device.index
+        handle = ctypes.c_void_p()
+        L_ = _lib.lib()
+        with torch.cuda.device(self.device):
+            _lib.check(L_.lms_paged_write_plan_create(*args, ctypes.byref(handle)))
+        self._handle = handle
+        self._run = L_.lms_write_plan_run
+        self._destroy = L_.lms_write_plan_destroy
+
+    def run(self, stream: Optional[int] = None) -> None:
+        """Enqueues the append on `stream` (a raw ``cudaStream_t`` value; default: the current
+        stream of the plan's device, which must be the current device)."""
+        if stream is None:
+            stream = _raw_stream(self._index) if _raw_stream is not None else \
+                torch.cuda.current_stream(self.device).cuda_stream
+        rc = self._run(self._handle, stream)
+        if rc:
+            _lib.check(rc)
+
+    def __del__(self):
+        h = getattr(self, "_handle", None)
+        if h:
+            self._destroy(h)
+            self._handle = None
+
+
+_PAGED_PLANS: Dict[tuple, PagedWritePlan] = {}
+_PAGED_PLANS_MAX = 2048
+
+
+def append_paged_kv_cache(
+    append_key: torch.Tensor,
+    append_value: torch.Tensor,
+    batch_indices: torch.Tensor,
+    positions: torch.Tensor,
+    paged_kv_cache,
+    kv_indices: torch.Tensor,
+    kv_indptr: torch.Tensor,
+    kv_last_page_len: Optional[torch.Tensor] = None,
+    kv_layout: str = "NHD",
+) -> None:
+    """Drop-in for ``flashinfer.append_paged_kv_cache`` as LMServe calls it
+    (``models/layers/attention.py:76-85``): same argument order and meaning, same in-place
+    result, so the call site changes only its import.
+
+    ``append_key``/``append_value``: ``[T, H, D]``; ``batch_indices``/``positions``: int32
+    ``[T]`` (request index and position of every appended token, as produced by
+    ``flashinfer.get_batch_indices_positions`` at ``model_worker.py:425-433``);
+    ``paged_kv_cache``: one layer's ``[num_pages, 2, page_size, H, D]`` tensor, or a
+    ``(k_cache, v_cache)`` pair of ``[num_pages, page_size, H, D]`` tensors; ``kv_indices`` /
+    ``kv_indptr``: int32 page table in CSR form.  ``kv_last_page_len`` is accepted and ignored
+    (the write does not need it).  Only the ``"NHD"`` layout, the one LMServe uses.
+
+    This runs once per layer per step with the same buffers, so the validated call is kept as
+    a :class:`PagedWritePlan` keyed on everything the validation looked at (addresses, shapes,
+    strides, dtypes); a repeat call is a dictionary lookup and one C call.
+    """
+    tensor_cache = type(paged_kv_cache) is torch.Tensor
+    if tensor_cache:
+        c0, c1 = paged_kv_cache, paged_kv_cache
+    else:
+        c0, c1 = paged_kv_cache
+    key = (append_key.data_ptr(), append_value.data_ptr(), batch_indices.data_ptr(),
+           positions.data_ptr(), c0.data_ptr(), c1.data_ptr(), kv_indices.data_ptr(),
+           kv_indptr.data_ptr(), append_key.shape, append_key.stride(), append_value.shape,
+           append_value.stride(), c0.shape, c0.stride(), c1.shape, c1.stride(),
+           append_key.dtype, append_value.dtype, c0.dtype, c1.dtype,
+           batch_indices.dtype, positions.dtype, kv_indices.dtype, kv_indptr.dtype,
+           batch_indices.shape, positions.shape, kv_indices.is_contiguous(), kv_indptr.shape,
+           c0.device, append_key.device, append_value.device, batch_indices.device,
+           positions.device, kv_indices.device, kv_indptr.device, tensor_cache, kv_layout)
+    plan = _PAGED_PLANS.get(key)
+    if plan is None:
+        if append_key.shape[0] == 0 and append_key.dim() == 3:
+            _prepare_paged(append_key, append_value, batch_indices, positions, paged_kv_cache,
+                           kv_indices, kv_indptr, kv_layout)
+            return
+        plan = PagedWritePlan(append_key, append_value, batch_indices, positions, paged_kv_cache,
+                              kv_indices, kv_indptr, kv_last_page_len, kv_layout)
+        if len(_PAGED_PLANS) >= _PAGED_PLANS_MAX:
+            _PAGED_PLANS.clear()
+        _PAGED_PLANS[key] = plan
+    idx = plan._index
+    if idx == torch.cuda.current_device():
+        plan.run()
+    else:
+        with torch.cuda.device(idx):
+            plan.run()
 
 
 def _prepare_write(key, value, kv_caches, slot_mapping):
@@ -501,6 +580,21 @@ def copy_blocks_no_alloc(
             arr.ctypes.data, arr.shape[0], _stream_ptr(dev)))
 
 
+_STAGING: Dict[Tuple[int, str], torch.Tensor] = {}
+
+
+def _default_staging(dev: torch.device, direction: str, min_bytes: int) -> torch.Tensor:
+    """One staging buffer per device and direction for callers that pass none (128 MiB, or
+    twice a block when that is more); allocated on first use, kept for the process."""
+    key = (dev.index if dev.index is not None else torch.cuda.current_device(), direction)
+    want = max(128 << 20, int(min_bytes))
+    t = _STAGING.get(key)
+    if t is None or t.numel() < want:
+        t = torch.empty(want, dtype=torch.uint8, device=dev)
+        _STAGING[key] = t
+    return t
+
+
 def swap_blocks(
     gpu_kv_caches: torch.Tensor,
     host_pool,
@@ -508,6 +602,7 @@ def swap_blocks(
     direction: str,
     layers: Optional[Tuple[int, int]] = None,
     engine: str = "kernel",
+    staging: Optional[torch.Tensor] = None,
 ) -> None:
     """Moves whole blocks between the GPU cache and a pinned host pool.
 
@@ -523,7 +618,10 @@ def swap_blocks(
     (``lms_swap_blocks_dma``; needs a host-side pair table): it uses no SM, so GEMMs that run
     at the same time keep the whole GPU — measured against a stream of 8192^3 bf16 GEMMs: the
     built-in 3-CTA copy kernel costs them about 10 %, copy grids of 5 CTAs and more 85 % and
-    upwards, the copy-engine form nothing.
+    upwards, the copy-engine form nothing.  ``engine="staged"`` gathers groups of blocks into
+    ``staging`` (a device tensor of the caller, at least two blocks' worth of bytes; 128 MiB
+    and more is sensible) and lets the copy engines move whole host blocks in one transfer each
+    (``lms_swap_blocks_staged``): the form for swapping many whole blocks at the full PCIe rate.
     """
     _require_cuda("gpu_kv_caches", gpu_kv_caches)
     if direction not in ("out", "in"):
@@ -535,14 +633,29 @@ def swap_blocks(
     l0, l1 = (0, L) if layers is None else layers
     if not (0 <= l0 <= l1 <= L):
         raise ValueError(f"layer range {layers} outside [0, {L}]")
-    if engine not in ("kernel", "dma"):
-        raise ValueError(f"engine must be 'kernel' or 'dma', got {engine!r}")
-    if engine == "dma" and isinstance(block_pairs, torch.Tensor) and block_pairs.is_cuda:
+    if engine not in ("kernel", "dma", "staged"):
+        raise ValueError(f"engine must be 'kernel', 'dma' or 'staged', got {engine!r}")
+    if engine != "kernel" and isinstance(block_pairs, torch.Tensor) and block_pairs.is_cuda:
         block_pairs = block_pairs.cpu()          # the copy engines are driven from the host
+    if engine == "staged":
+        if staging is None:
+            staging = _default_staging(dev, direction, 2 * (l1 - l0) * chunk)
+        elif not (isinstance(staging, torch.Tensor) and staging.is_cuda and staging.device == dev
+                  and staging.is_contiguous()):
+            raise ValueError("staging must be a contiguous tensor on the cache's device")
     on_device, _keep, ptr, n = _pair_table(block_pairs, dev)
     if n == 0 or l0 == l1:
         return
     L_ = _lib.lib()
+    if engine == "staged":
+        with _OnDevice(dev):
+            _lib.check(L_.lms_swap_blocks_staged(
+                _lib.LMS_SWAP_OUT if direction == "out" else _lib.LMS_SWAP_IN,
+                gpu_kv_caches.data_ptr(), layer_stride, block_stride,
+                host_pool.device_ptr, host_pool.block_stride, host_pool.layer_stride,
+                chunk, l0, l1, ptr, n, NB, host_pool.num_blocks,
+                staging.data_ptr(), staging.numel() * staging.element_size(), _stream_ptr(dev)))
+        return
     if engine == "dma":
         fn = L_.lms_swap_blocks_dma
     else:

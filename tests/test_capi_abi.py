@@ -46,7 +46,7 @@ def test_tuning_roundtrip_and_range():
     assert L.lms_get_tuning(_lib.TUNE_WRITE_VARIANT) == 2
     assert L.lms_set_tuning(_lib.TUNE_WRITE_VARIANT, -1) == 0
     assert L.lms_get_tuning(_lib.TUNE_WRITE_VARIANT) == -1
-    assert L.lms_set_tuning(_lib.TUNE_WRITE_VARIANT, 5) == _lib.LMS_ERR_RANGE
+    assert L.lms_set_tuning(_lib.TUNE_WRITE_VARIANT, 8) == _lib.LMS_ERR_RANGE
     assert L.lms_set_tuning(_lib.TUNE_COPY_VARIANT, 5) == _lib.LMS_ERR_RANGE
     assert L.lms_set_tuning(0, 1) == _lib.LMS_ERR_RANGE
     assert L.lms_set_tuning(99, 1) == _lib.LMS_ERR_RANGE

@@ -18,7 +18,9 @@ from oracle import cache_oracle
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
-VARIANTS = [0, 1, 2, 3, 4]  # tiled 16/32-byte vectors, bulk (TMA) copies, untiled 32/16-byte
+# tiled 16/32-byte vectors, bulk (TMA) copies, untiled 32/16-byte, one-wave (K, V) pairs,
+# one-wave independent vectors, persistent (K, V) pairs
+VARIANTS = [0, 1, 2, 3, 4, 5, 6, 7]
 
 
 @pytest.fixture(autouse=True)
@@ -36,6 +38,30 @@ def set_variant(v):
     assert L.lms_set_tuning(_lib.TUNE_WRITE_VARIANT, v) == 0
     for key in (_lib.TUNE_COPY_VARIANT, _lib.TUNE_XFER_VARIANT):
         assert L.lms_set_tuning(key, min(v, 3)) == 0
+
+
+@pytest.mark.parametrize("per_thread", [1, 2, 4])
+@pytest.mark.parametrize("variant", [5, 6, 7])
+def test_one_wave_write_kernels_units_per_thread(variant, per_thread):
+    """The one-wave write kernels with 1, 2 and 4 units per thread: 2 KiB rows, 256-byte rows,
+    rows that are not a power of two, a per-layer slot table and a persistent grid of one CTA."""
+    L = _lib.lib()
+    set_variant(variant)
+    L.lms_set_tuning(_lib.TUNE_WRITE_VPT, per_thread)
+    shape = W.SHAPES["llama31_8b"].scaled(num_layers=3, num_blocks=512)
+    w = W.make_decode_write(shape, 53, 16, 160, seed=131)
+    slots = w.slot_mapping.copy()
+    slots[5] = -1
+    run_layers_case(shape, slots, 141)
+    run_layers_case(shape, slots, 142, slot_per_layer=True)
+    shape = W.SHAPES["llama31_70b_tp8"].scaled(num_layers=7, num_blocks=8192)
+    w = W.make_decode_write(shape, 301, 64, 300, seed=135)
+    run_layers_case(shape, w.slot_mapping, 145)
+    odd = W.KVShape("odd", num_layers=2, num_blocks=9, num_kv_heads=5, head_dim=24, block_size=7,
+                    dtype="bf16")
+    rng = np.random.default_rng(146)
+    slots = rng.permutation(9 * 7)[:41].astype(np.int64)
+    run_layers_case(odd, slots, 147)
 
 
 # ----------------------------------------------------------------- golden vectors
@@ -442,6 +468,53 @@ def test_append_paged_kv_cache_vs_oracle(variant):
     with pytest.raises(TypeError, match="int32"):
         cache_ops.append_paged_kv_cache(to_tensor(key, "bf16", DEV), to_tensor(value, "bf16", DEV),
                                         dev(batch).long(), dev(pos), got, dev(indices), dev(indptr))
+
+
+@pytest.mark.parametrize("variant", [3, 5, 7])
+def test_append_paged_decode_step_plan_is_reused_and_guess_may_be_wrong(variant):
+    """A decode step (one token per request): token t belongs to request t, the case the
+    kernel's early fetch of kv_indptr[t] is made for.  The same call is repeated after the
+    index tensors were refilled in place (the cached plan must read the new contents), and
+    with the requests in shuffled order, where the guess is wrong for most tokens."""
+    set_variant(variant)
+    n = 57
+    shape, key, value, cache, batch, pos, indices, indptr = paged_case(111, n, 1, num_blocks=900)
+    dev = lambda a: torch.from_numpy(a).to(DEV)
+    k, v = to_tensor(key, "bf16", DEV), to_tensor(value, "bf16", DEV)
+    d_batch, d_pos, d_ind, d_ptr = dev(batch), dev(pos), dev(indices), dev(indptr)
+    got = to_tensor(cache, "bf16", DEV)
+    want = cache.copy()
+    before = len(cache_ops._PAGED_PLANS)
+    cache_ops.append_paged_kv_cache(k, v, d_batch, d_pos, got, d_ind, d_ptr, None)
+    cache_oracle.append_paged_kv_cache(key, value, batch, pos, want, indices, indptr)
+    torch.cuda.synchronize()
+    assert np.array_equal(to_words(got), want)
+    assert len(cache_ops._PAGED_PLANS) == before + 1
+    # next step: same buffers, new contents - requests in shuffled order, one padded row
+    perm = np.random.default_rng(5).permutation(n).astype(np.int32)
+    batch2, pos2 = batch[perm].copy(), (pos[perm] + 1).astype(np.int32)
+    # a position one further may need a page the request does not own: keep it inside
+    room = (indptr[1:] - indptr[:-1])[batch2] * 16
+    pos2 = np.minimum(pos2, room - 1).astype(np.int32)
+    batch2[7] = -1
+    d_batch.copy_(dev(batch2))
+    d_pos.copy_(dev(pos2))
+    cache_ops.append_paged_kv_cache(k, v, d_batch, d_pos, got, d_ind, d_ptr, None)
+    cache_oracle.append_paged_kv_cache(key, value, batch2, pos2, want, indices, indptr)
+    torch.cuda.synchronize()
+    assert np.array_equal(to_words(got), want)
+    assert len(cache_ops._PAGED_PLANS) == before + 1          # the plan was reused
+    # an explicit plan, run on a side stream
+    plan = cache_ops.PagedWritePlan(k, v, d_batch, d_pos, got, d_ind, d_ptr)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    got.copy_(to_tensor(cache, "bf16", DEV))
+    side.wait_stream(torch.cuda.current_stream())
+    plan.run(side.cuda_stream)
+    side.synchronize()
+    want2 = cache.copy()
+    cache_oracle.append_paged_kv_cache(key, value, batch2, pos2, want2, indices, indptr)
+    assert np.array_equal(to_words(got), want2)
 
 
 def test_append_paged_kv_cache_matches_flashinfer():
