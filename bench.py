@@ -36,7 +36,7 @@ import torch
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
-from lmserve_b200 import workloads as W  # noqa: E402
+import workloads as W  # noqa: E402
 from lmserve_b200.disagg import Comm  # noqa: E402
 
 METRIC = "kv_cache_write_bandwidth"

@@ -1,7 +1,11 @@
 """gRPC face of the KV worker: a servicer that is wire-compatible with LMServe's ``KVWorker``
 service (``proto/worker.proto:19-27,78-117``) and backed by :class:`lmserve_b200.kv_worker.KVWorker`,
-so the unchanged Rust ``KVWorkerGroup`` (``runtime/src/llm_engine/worker.rs:420-548``) can drive the
-B200 kernels over the same Unix socket it uses today.
+so the Rust ``KVWorkerGroup`` (``runtime/src/llm_engine/worker.rs:420-548``) can drive the B200
+kernels over the same Unix socket and messages it uses today.  One thing changes on the engine
+side: ``GetDescriptors`` / ``PushKV`` / ``PullKV`` carry **GPU** block ids, because blocks move
+cache to cache; the reference's engine reserves and pins *host* blocks for a transfer
+(``engine.rs:272-280,425-430``) and has to reserve GPU blocks instead.  The worker range-checks
+every id against the two caches and answers ``success=False`` for ids that do not fit.
 
 The reference generates its message classes with ``protoc`` (``llm_worker/pb/``, git-ignored).
 ``protoc`` is not required here: the handful of messages the KV service uses are declared below
@@ -135,7 +139,10 @@ class KVWorkerService:
         return AddRemoteAgentMetadataResponse(peer_name=request.agent_name)
 
     def GetDescriptors(self, request, context):
-        return GetDescriptorsResponse(descs=self.worker.get_descriptors(list(request.block_ids)))
+        try:
+            return GetDescriptorsResponse(descs=self.worker.get_descriptors(list(request.block_ids)))
+        except IndexError as e:
+            context.abort(grpc.StatusCode.INVALID_ARGUMENT, str(e))
 
     def PushKV(self, request, context):
         ok = self.worker.push_kv(request.peer_name, request.kv_descs, list(request.block_ids))

@@ -1,17 +1,19 @@
 """Host-side mirror of LMServe's ``KVWorker`` (``runtime/worker/llm_worker/kv_worker.py``)
 for the parts that move KV blocks through the GPU: the pinned host pool, the
-GPU<->host swap in both directions with the per-layer event handshake, and the
+GPU<->host swap in both directions with the per-layer event + queue handshake, and the
 prefill->decode push — here a direct GPU->GPU store over NVLink instead of the
 reference's NIXL/UCX host-to-host write.
 
-Not mirrored (no GPU data path): the disk tier (``kv_worker.py:229-247,297-322``)
-and the NIXL agent bookkeeping.
+The disk tier (``kv_worker.py:229-247,297-322``) is kept as the reference's host-only numpy
+copies so that its four ``copy_kv`` directions keep working; the NIXL agent bookkeeping is
+not mirrored.
 """
 from __future__ import annotations
 
 import ctypes
 import enum
-import pickle
+import queue as _queue
+import struct
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence
 
@@ -142,6 +144,10 @@ class HostPool:
             pass
 
 
+IPC_HANDLE_BYTES = 64      # sizeof(cudaIpcMemHandle_t), LMS_IPC_HANDLE_BYTES of the C header
+HANDSHAKE_TIMEOUT_S = 60.0  # how long either side waits for the other's per-layer token
+
+
 @dataclass
 class CacheDescriptor:
     """What a decode-side worker hands to a prefill-side worker so it can push blocks:
@@ -157,38 +163,84 @@ class CacheDescriptor:
     block_stride: int
     chunk_bytes: int
     block_ids: List[int]
+    # An IPC handle cannot be opened by the process that exported it.  The exporter's pid and
+    # the cache's address let a worker of the SAME process (two workers on threads, or on two
+    # GPUs of one process) use the memory directly; they are honoured only for caches this
+    # process has itself exported (``_LOCAL_EXPORTS``).
+    pid: int = 0
+    address: int = 0
+
+    # Wire form: a fixed little-endian header (magic, ten integers, the 64-byte IPC handle)
+    # followed by the reserved block ids as int64.  Nothing in it is executable or typed by the
+    # sender: a malformed buffer raises ValueError.
+    _HEADER = struct.Struct("<4s10q64s")
+    _MAGIC = b"LMS2"
 
     def serialize(self) -> bytes:
-        return pickle.dumps(self.__dict__)
+        if len(self.handle) != IPC_HANDLE_BYTES:
+            raise ValueError("the IPC handle must be 64 bytes")
+        ids = np.asarray(self.block_ids, dtype="<i8").reshape(-1)
+        head = self._HEADER.pack(self._MAGIC, self.offset, self.device_index, self.num_layers,
+                                 self.num_blocks, self.layer_stride, self.block_stride,
+                                 self.chunk_bytes, ids.size, self.pid, self.address,
+                                 bytes(self.handle))
+        return head + ids.tobytes()
 
     @classmethod
     def deserialize(cls, data: bytes) -> "CacheDescriptor":
-        return cls(**pickle.loads(data))
+        data = bytes(data)
+        if len(data) < cls._HEADER.size:
+            raise ValueError("cache descriptor is truncated")
+        (magic, offset, device_index, num_layers, num_blocks, layer_stride, block_stride,
+         chunk_bytes, n_ids, pid, address, handle) = cls._HEADER.unpack_from(data)
+        if magic != cls._MAGIC:
+            raise ValueError("not a cache descriptor")
+        if n_ids < 0 or len(data) != cls._HEADER.size + 8 * n_ids:
+            raise ValueError("cache descriptor length does not match its block count")
+        if min(offset, device_index, num_layers, num_blocks, layer_stride, block_stride, chunk_bytes,
+               pid, address) < 0:
+            raise ValueError("cache descriptor holds a negative size")
+        ids = np.frombuffer(data, dtype="<i8", count=n_ids, offset=cls._HEADER.size)
+        return cls(handle, offset, device_index, num_layers, num_blocks, layer_stride,
+                   block_stride, chunk_bytes, ids.tolist(), pid, address)
+
+
+# address -> device index of every cache this process has described with get_descriptors
+_LOCAL_EXPORTS: Dict[int, int] = {}
 
 
 class PeerCache:
-    """Another process's GPU cache mapped into this process (``lms_ipc_open``)."""
+    """Another worker's GPU cache made addressable here: mapped through its CUDA IPC handle
+    (``lms_ipc_open``) when it belongs to another process, used in place (with peer access
+    enabled when it is on another GPU) when this process exported it."""
 
     def __init__(self, desc: CacheDescriptor):
+        import os
         self.desc = desc
         self.num_layers = desc.num_layers
         self.num_blocks = desc.num_blocks
         self.layer_stride = desc.layer_stride
         self.block_stride = desc.block_stride
         self.chunk_bytes = desc.chunk_bytes
-        buf = ctypes.create_string_buffer(desc.handle, _lib_handle_bytes())
+        self._mapped = False
+        if desc.pid == os.getpid() and desc.pid != 0:
+            if _LOCAL_EXPORTS.get(desc.address) != desc.device_index:
+                raise ValueError("descriptor names this process but no cache it has exported")
+            if desc.device_index != torch.cuda.current_device():
+                _lib.check(_lib.lib().lms_peer_enable(desc.device_index))
+            self.device_ptr = desc.address
+            return
+        buf = ctypes.create_string_buffer(desc.handle, IPC_HANDLE_BYTES)
         out = ctypes.c_void_p()
         _lib.check(_lib.lib().lms_ipc_open(buf, desc.offset, ctypes.byref(out)))
         self.device_ptr = out.value
+        self._mapped = True
 
     def close(self) -> None:
         if getattr(self, "device_ptr", None):
-            _lib.check(_lib.lib().lms_ipc_close(self.device_ptr, self.desc.offset))
+            if self._mapped:
+                _lib.check(_lib.lib().lms_ipc_close(self.device_ptr, self.desc.offset))
             self.device_ptr = None
-
-
-def _lib_handle_bytes() -> int:
-    return 64
 
 
 @dataclass
@@ -197,9 +249,14 @@ class KVWorkerParams:
     its per-layer events: the GPU-facing fields of ``KVWorkerParams`` (``kv_worker.py:34-45``).
     ``kv_cache_metadata`` is the tuple ``UntypedStorage._share_cuda_()`` returns
     (``model_worker.py:284``); the event handles come from ``Event.ipc_handle()`` of events
-    created with ``interprocess=True`` (``model_worker.py:232-251,285-290``).  The queues of the
-    reference carry only wake-up tokens for its polling loops; here ordering is by the events
-    themselves, so no queue is needed."""
+    created with ``interprocess=True`` (``model_worker.py:232-251,285-290``).
+
+    ``model_queue`` / ``kv_queue`` are the reference's two token queues
+    (``model_worker.py:239-240``) and are needed for the same reason: a stream wait binds to the
+    most recent *record* of the event at the moment the wait is issued (and does nothing if the
+    event was never recorded), so the waiting side must not issue its wait before the other
+    side has issued this step's record.  The recorder puts one token per layer after its
+    ``record``; the waiter takes one token before its ``wait_event``."""
     kv_cache_metadata: tuple
     cache_shape: tuple            # (num_layers, num_gpu_blocks, 2, block_size, H, D)
     dtype: torch.dtype
@@ -209,18 +266,22 @@ class KVWorkerParams:
     post_event_handles: Sequence[bytes] = ()
     num_disk_blocks: int = 0
     disk_kv_cache_file: Optional[str] = None
+    model_queue: object = None    # KV process -> model: "pre_events[l] of this step is recorded"
+    kv_queue: object = None       # model -> KV process: "post_events[l] of this step is recorded"
 
     @classmethod
     def from_cache(cls, kv_caches: torch.Tensor, num_host_blocks: int = 0,
                    pre_events: Sequence[torch.cuda.Event] = (),
-                   post_events: Sequence[torch.cuda.Event] = ()) -> "KVWorkerParams":
+                   post_events: Sequence[torch.cuda.Event] = (),
+                   model_queue=None, kv_queue=None) -> "KVWorkerParams":
         """Called in the model process (``ModelWorker.init_cache``, ``model_worker.py:278-306``)."""
         cache_ops._require_cuda("kv_caches", kv_caches)
         if not kv_caches.is_contiguous() or kv_caches.storage_offset() != 0:
             raise ValueError("the shared cache must be a whole contiguous allocation")
         return cls(kv_caches.untyped_storage()._share_cuda_(), tuple(kv_caches.shape), kv_caches.dtype,
                    num_host_blocks, kv_caches.device.index,
-                   [e.ipc_handle() for e in pre_events], [e.ipc_handle() for e in post_events])
+                   [e.ipc_handle() for e in pre_events], [e.ipc_handle() for e in post_events],
+                   model_queue=model_queue, kv_queue=kv_queue)
 
 
 def cache_block_counts(gpu_cache_size: int, host_cache_size: int, num_layers: int, num_kv_heads: int,
@@ -235,16 +296,43 @@ def cache_block_counts(gpu_cache_size: int, host_cache_size: int, num_layers: in
     return int(gpu_cache_size) // per_block, int(host_cache_size) // per_block, kv_block_size
 
 
+def _take_token(q, what: str) -> None:
+    """Blocks until the other side has put its token for `what` (or raises TimeoutError)."""
+    try:
+        q.get(timeout=HANDSHAKE_TIMEOUT_S)
+    except _queue.Empty:
+        raise TimeoutError(f"no token for {what} within {HANDSHAKE_TIMEOUT_S:.0f} s: the other "
+                           "side of the layer handshake did not record its event") from None
+
+
 @dataclass
 class KVWorkerHandle:
-    """The model process's end of the layer handshake: ``KVWorkerHandle`` of ``kv_worker.py:25-32``
-    without its two wake-up queues (the events order the streams by themselves).  Layer ``i`` of
-    the forward pass waits for ``pre_events[i]`` (its blocks have been swapped in) and records
-    ``post_events[i]`` when it has written its KV (they may be swapped out or pushed)."""
+    """The model process's end of the layer handshake: ``KVWorkerHandle`` of
+    ``kv_worker.py:25-32``.  Layer ``i`` of the forward pass waits for ``pre_events[i]`` (its
+    blocks have been swapped in) and records ``post_events[i]`` when it has written its KV
+    (they may be swapped out or pushed).  With the queues set (always, when the KV worker runs
+    in another process or thread) the pre-hook first takes a token from ``model_queue`` — the
+    KV worker puts it after recording ``pre_events[i]`` — and the post-hook puts a token on
+    ``kv_queue`` after its record, exactly as ``model_worker.py:259-270``; without that the
+    stream wait could be issued before this step's record and bind to the previous step's."""
     pre_events: List[torch.cuda.Event]
     post_events: List[torch.cuda.Event]
     enable_wait_before_execute: bool = False
     enable_record_after_execute: bool = False
+    model_queue: object = None
+    kv_queue: object = None
+
+    def wait_before_layer(self, i: int, stream=None) -> None:
+        """What the pre-hook of layer `i` does (``model_worker.py:259-263``)."""
+        if self.model_queue is not None:
+            _take_token(self.model_queue, f"pre_events[{i}]")
+        (stream or torch.cuda.current_stream()).wait_event(self.pre_events[i])
+
+    def record_after_layer(self, i: int, stream=None) -> None:
+        """What the post-hook of layer `i` does (``model_worker.py:265-270``)."""
+        self.post_events[i].record(stream or torch.cuda.current_stream())
+        if self.kv_queue is not None:
+            self.kv_queue.put(b"")
 
     def register_hooks(self, attn_layers, stream: Optional[torch.cuda.Stream] = None) -> list:
         """Forward pre / post hooks on the attention modules, as ``model_worker.py:253-275``:
@@ -255,11 +343,11 @@ class KVWorkerHandle:
         for i, layer in enumerate(attn_layers):
             def pre_hook(mod, args, i=i):
                 if self.enable_wait_before_execute:
-                    (stream or torch.cuda.current_stream()).wait_event(self.pre_events[i])
+                    self.wait_before_layer(i, stream)
 
             def post_hook(mod, args, output, i=i):
                 if self.enable_record_after_execute:
-                    self.post_events[i].record(stream or torch.cuda.current_stream())
+                    self.record_after_layer(i, stream)
 
             handles.append(layer.register_forward_pre_hook(pre_hook))
             handles.append(layer.register_forward_hook(post_hook))
@@ -267,12 +355,14 @@ class KVWorkerHandle:
 
 
 def init_cache(gpu_cache_size: int, host_cache_size: int, *, num_layers: int, num_kv_heads: int,
-               head_dim: int, block_size: int, dtype: torch.dtype, device="cuda"):
+               head_dim: int, block_size: int, dtype: torch.dtype, device="cuda", mp_context="spawn"):
     """``ModelWorker.init_cache`` (``model_worker.py:200-308``) for the GPU and host tiers:
     allocates the paged cache ``[L, num_gpu_blocks, 2, block_size, H, D]``, creates the per-layer
     interprocess events, and returns ``(kv_caches, handle, params)`` — the cache for the model,
     the :class:`KVWorkerHandle` for its hooks, and the :class:`KVWorkerParams` to send to the KV
-    process (``KVWorker.from_params``)."""
+    process (``KVWorker.from_params``).  The two token queues of the handshake are created in
+    the multiprocessing context `mp_context` (a name or a context object; ``None`` = no queues,
+    for a worker driven from the model's own thread) and travel inside ``params``."""
     num_gpu_blocks, num_host_blocks, _ = cache_block_counts(
         gpu_cache_size, host_cache_size, num_layers, num_kv_heads, head_dim, block_size, dtype)
     if num_gpu_blocks <= 0:
@@ -285,8 +375,14 @@ def init_cache(gpu_cache_size: int, host_cache_size: int, *, num_layers: int, nu
                                 dtype=dtype, device=dev)
         pre = [torch.cuda.Event(interprocess=True) for _ in range(num_layers)]
         post = [torch.cuda.Event(interprocess=True) for _ in range(num_layers)]
-    handle = KVWorkerHandle(pre, post)
-    return kv_caches, handle, KVWorkerParams.from_cache(kv_caches, num_host_blocks, pre, post)
+    model_queue = kv_queue = None
+    if mp_context is not None:
+        import torch.multiprocessing as tmp
+        ctx = tmp.get_context(mp_context) if isinstance(mp_context, str) else mp_context
+        model_queue, kv_queue = ctx.Queue(), ctx.Queue()
+    handle = KVWorkerHandle(pre, post, model_queue=model_queue, kv_queue=kv_queue)
+    return kv_caches, handle, KVWorkerParams.from_cache(kv_caches, num_host_blocks, pre, post,
+                                                        model_queue, kv_queue)
 
 
 def open_disk_pool(path: str, shape) -> np.ndarray:
@@ -318,14 +414,17 @@ class KVWorker:
 
     def __init__(self, name: str, gpu_kv_caches: torch.Tensor, num_host_blocks: int = 0,
                  swap_engine: str = "kernel", num_disk_blocks: int = 0,
-                 disk_kv_cache_file: Optional[str] = None, num_disk_copy_workers: int = 4):
+                 disk_kv_cache_file: Optional[str] = None, num_disk_copy_workers: int = 4,
+                 staging_bytes: int = 256 << 20):
         cache_ops._require_cuda("gpu_kv_caches", gpu_kv_caches)
-        if swap_engine not in ("kernel", "dma"):
-            raise ValueError("swap_engine must be 'kernel' or 'dma'")
-        # "kernel": the sm_100a gather/scatter kernel on 3 CTAs - full PCIe rate even when
-        # launched once per layer, at a cost of about 10 % to concurrent full-SM GEMMs.
+        if swap_engine not in ("kernel", "dma", "staged"):
+            raise ValueError("swap_engine must be 'kernel', 'dma' or 'staged'")
+        # "kernel": the sm_100a gather/scatter kernel on 3 CTAs - 0.92 of the PCIe memcpy rate
+        # even when launched once per layer, at a cost of about 10 % to concurrent full-SM GEMMs.
         # "dma": copy engines only, no SM is touched; full rate needs many layers per launch
         # (one 64 KiB copy per layer and block, the reference's pattern, reaches 13 GB/s).
+        # "staged": whole-block swaps through a device staging ring and one DMA transfer per
+        # host block; swaps that are pipelined layer by layer fall back to the kernel.
         self.swap_engine = swap_engine
         self.name = name
         self.gpu_kv_caches = gpu_kv_caches
@@ -339,6 +438,14 @@ class KVWorker:
             self.dtoh_stream = torch.cuda.Stream()
             self.htod_stream = torch.cuda.Stream()
             self.push_stream = torch.cuda.Stream()
+        self._staging_bytes = int(staging_bytes)
+        self._staging: Dict[str, torch.Tensor] = {}
+        # the token queues of the layer handshake (None: the model runs in this thread and
+        # issues its records before the worker's waits by construction)
+        self.model_queue = None
+        self.kv_queue = None
+        self.pre_events: List[torch.cuda.Event] = []
+        self.post_events: List[torch.cuda.Event] = []
         self._peers: Dict[str, PeerCache] = {}
         self.COPY_KV_OP_MAP = {
             (Device.GPU, Device.Host): self.save_kv_blocks_to_host,
@@ -359,10 +466,12 @@ class KVWorker:
             self.COPY_KV_OP_MAP[(Device.Disk, Device.Host)] = self.load_kv_blocks_from_disk
 
     @classmethod
-    def from_params(cls, name: str, params: KVWorkerParams) -> "KVWorker":
+    def from_params(cls, name: str, params: KVWorkerParams, **kw) -> "KVWorker":
         """Built in the KV process: maps the model process's cache through CUDA IPC
-        (``kv_worker.py:104-108``) and opens its interprocess events (``kv_worker.py:140-147``).
-        The events are available as ``worker.pre_events`` / ``worker.post_events``."""
+        (``kv_worker.py:104-108``), opens its interprocess events (``kv_worker.py:140-147``) and
+        keeps its two token queues (``kv_worker.py:149-154``).  The events are available as
+        ``worker.pre_events`` / ``worker.post_events``; swaps that are given these events use the
+        queues for the host side of the handshake."""
         dev = torch.device("cuda", params.device_index)
         with torch.cuda.device(dev):
             storage = torch.UntypedStorage._new_shared_cuda(*params.kv_cache_metadata)
@@ -370,9 +479,11 @@ class KVWorker:
             cache.set_(storage)
             cache = cache.view(*params.cache_shape)
             worker = cls(name, cache, params.num_host_blocks, num_disk_blocks=params.num_disk_blocks,
-                         disk_kv_cache_file=params.disk_kv_cache_file)
+                         disk_kv_cache_file=params.disk_kv_cache_file, **kw)
             worker.pre_events = [torch.cuda.Event.from_ipc_handle(dev, h) for h in params.pre_event_handles]
             worker.post_events = [torch.cuda.Event.from_ipc_handle(dev, h) for h in params.post_event_handles]
+        worker.model_queue = params.model_queue
+        worker.kv_queue = params.kv_queue
         return worker
 
     # -- swap -----------------------------------------------------------------
@@ -382,9 +493,10 @@ class KVWorker:
         """Host -> GPU fetch (``kv_worker.py:249-270``).
 
         With ``pre_events`` the fetch runs ``layers_per_launch`` layers at a time
-        (default 1, like the reference) and records ``pre_events[l]`` on the copy
-        stream once layer ``l`` has landed, so the forward pass can wait per layer;
-        without them it is one launch over all layers.
+        (default 1, like the reference) and, once layer ``l`` has been enqueued, records
+        ``pre_events[l]`` on the copy stream and puts one token on ``model_queue`` (when the
+        worker has one), so the forward pass can wait per layer; without them it is one launch
+        over all layers.  As in the reference nothing is recorded for an empty request.
         """
         self._swap(block_mappings, "in", stream or self.htod_stream, pre_events, None,
                    layers_per_launch)
@@ -394,8 +506,10 @@ class KVWorker:
                                layers_per_launch: Optional[int] = None) -> None:
         """GPU -> host write-through (``kv_worker.py:272-295``).
 
-        With ``post_events`` the copy stream waits for ``post_events[l]`` (recorded by
-        the model after layer ``l``'s attention) before layer ``l`` is copied.
+        With ``post_events`` the worker takes the model's token for layer ``l`` from
+        ``kv_queue`` (when it has one; the model puts it after recording, so the record has been
+        issued), makes the copy stream wait for ``post_events[l]`` (recorded by the model after
+        layer ``l``'s attention) and then copies layer ``l``.
         """
         self._swap(block_mappings, "out", stream or self.dtoh_stream, None, post_events,
                    layers_per_launch)
@@ -425,6 +539,14 @@ class KVWorker:
         self._disk_copy(block_mappings, self.host_pool.array, self.disk_kv_caches,
                         (self.dtoh_stream, self.htod_stream))
 
+    def _staging_for(self, direction: str) -> torch.Tensor:
+        t = self._staging.get(direction)
+        if t is None:
+            want = max(self._staging_bytes, 2 * self.num_layers * self.chunk_bytes)
+            t = torch.empty(want, dtype=torch.uint8, device=self.device)
+            self._staging[direction] = t
+        return t
+
     def _swap(self, block_mappings, direction, stream, pre_events, post_events, group) -> None:
         if self.host_pool is None:
             raise RuntimeError("this KVWorker was created without a host pool")
@@ -435,23 +557,34 @@ class KVWorker:
         L = self.num_layers
         with torch.cuda.device(self.device), torch.cuda.stream(stream):
             engine = self.swap_engine
+            if events is None:
+                if engine == "staged":
+                    cache_ops.swap_blocks(self.gpu_kv_caches, self.host_pool, pairs_np, direction,
+                                          engine="staged", staging=self._staging_for(direction))
+                    return
+                pairs = pairs_np if engine == "dma" else cache_ops._pairs_on_device(pairs_np, self.device)
+                cache_ops.swap_blocks(self.gpu_kv_caches, self.host_pool, pairs, direction, engine=engine)
+                return
+            if engine == "staged":
+                engine = "kernel"     # layer by layer every transfer is one chunk: the kernel wins
             # the kernel reads the table on the device (uploaded once for all layer launches);
             # the copy engines are driven from the host table
             pairs = pairs_np if engine == "dma" else cache_ops._pairs_on_device(pairs_np, self.device)
-            if events is None:
-                cache_ops.swap_blocks(self.gpu_kv_caches, self.host_pool, pairs, direction, engine=engine)
-                return
             step = max(1, int(group or 1))
             for l0 in range(0, L, step):
                 l1 = min(L, l0 + step)
                 if post_events is not None:
                     for l in range(l0, l1):
+                        if self.kv_queue is not None:
+                            _take_token(self.kv_queue, f"post_events[{l}]")
                         stream.wait_event(post_events[l])
                 cache_ops.swap_blocks(self.gpu_kv_caches, self.host_pool, pairs, direction,
                                       layers=(l0, l1), engine=engine)
                 if pre_events is not None:
                     for l in range(l0, l1):
                         pre_events[l].record(stream)
+                        if self.model_queue is not None:
+                            self.model_queue.put(b"")
 
     def copy_kv(self, block_mappings, src: Device, dst: Device, **kw) -> None:
         """``KVWorker.copy_kv`` (``kv_worker.py:336-346``): dispatch on (src, dst)."""
@@ -463,15 +596,55 @@ class KVWorker:
     # -- prefill -> decode ----------------------------------------------------
     def get_descriptors(self, block_ids: Sequence[int]) -> bytes:
         """Serialized descriptor of this worker's GPU cache and the reserved blocks
-        (role of ``kv_worker.py:348-356``)."""
-        handle = ctypes.create_string_buffer(_lib_handle_bytes())
+        (role of ``kv_worker.py:348-356``).  The ids are *GPU* block ids of this worker: the
+        transfer goes cache to cache, so an engine that drives it reserves GPU blocks on the
+        decode side where the reference's engine reserves host blocks."""
+        ids = [int(b) for b in block_ids]
+        if ids and (min(ids) < 0 or max(ids) >= self.num_gpu_blocks):
+            raise IndexError(f"reserved block id outside the cache of {self.num_gpu_blocks} blocks")
+        handle = ctypes.create_string_buffer(IPC_HANDLE_BYTES)
         offset = ctypes.c_int64()
         with torch.cuda.device(self.device):
             _lib.check(_lib.lib().lms_ipc_export(self.gpu_kv_caches.data_ptr(), handle,
                                                  ctypes.byref(offset)))
+        import os
+        address = self.gpu_kv_caches.data_ptr()
+        _LOCAL_EXPORTS[address] = self.device.index
         return CacheDescriptor(handle.raw, offset.value, self.device.index, self.num_layers,
                                self.num_gpu_blocks, self.layer_stride, self.block_stride,
-                               self.chunk_bytes, [int(b) for b in block_ids]).serialize()
+                               self.chunk_bytes, ids, os.getpid(), address).serialize()
+
+    def _transfer_table(self, remote_descs: bytes, block_ids: Sequence[int]):
+        """(descriptor, [n, 2] (local, remote) table) after every check the host can make: the
+        descriptor parses, the geometries agree, and every id lies inside its cache — a bad id
+        would otherwise overwrite another sequence's blocks on the peer without any error.
+        Raises ValueError with the reason."""
+        desc = CacheDescriptor.deserialize(remote_descs)
+        if desc.num_layers != self.num_layers or desc.chunk_bytes != self.chunk_bytes:
+            raise ValueError(f"cache geometries differ (peer {desc.num_layers} layers x {desc.chunk_bytes} B, "
+                             f"local {self.num_layers} x {self.chunk_bytes} B)")
+        if desc.block_stride < desc.chunk_bytes or desc.layer_stride < desc.chunk_bytes or \
+                desc.block_stride % 16 or desc.layer_stride % 16:
+            raise ValueError("peer descriptor has impossible strides")
+        pairs = build_push_pairs(block_ids, desc.block_ids)
+        if pairs.shape[0]:
+            lo, hi = pairs.min(axis=0), pairs.max(axis=0)
+            if lo[0] < 0 or hi[0] >= self.num_gpu_blocks:
+                raise ValueError(f"local block id outside the cache of {self.num_gpu_blocks} blocks")
+            if lo[1] < 0 or hi[1] >= desc.num_blocks:
+                raise ValueError(f"remote block id outside the peer cache of {desc.num_blocks} blocks")
+        return desc, pairs
+
+    def _peer(self, peer_name: str, desc: CacheDescriptor) -> PeerCache:
+        peer = self._peers.get(peer_name)
+        if peer is not None and (peer.desc.handle != desc.handle or peer.desc.offset != desc.offset
+                                 or peer.desc.address != desc.address):
+            peer.close()          # the peer re-allocated its cache: map the new one
+            peer = None
+        if peer is None:
+            peer = PeerCache(desc)
+            self._peers[peer_name] = peer
+        return peer
 
     def push_kv(self, peer_name: str, remote_descs: bytes, block_ids: Sequence[int],
                 stream: Optional[torch.cuda.Stream] = None, post_events=None,
@@ -483,17 +656,13 @@ class KVWorker:
         ``post_events`` (one event per layer, recorded by the model after it has written that
         layer's KV) the push is issued layer by layer behind the prefill instead of after it."""
         try:
-            desc = CacheDescriptor.deserialize(remote_descs)
             try:
-                pairs = build_push_pairs(block_ids, desc.block_ids)
-            except ValueError as e:
+                desc, pairs = self._transfer_table(remote_descs, block_ids)
+            except (ValueError, struct.error) as e:
                 print(f"Creating transfer failed. {e}")
                 return False
             with torch.cuda.device(self.device):
-                peer = self._peers.get(peer_name)
-                if peer is None:
-                    peer = PeerCache(desc)
-                    self._peers[peer_name] = peer
+                peer = self._peer(peer_name, desc)
                 s = stream or self.push_stream
                 with torch.cuda.stream(s):
                     if post_events is None:
@@ -507,10 +676,12 @@ class KVWorker:
                         for l0 in range(0, self.num_layers, step):
                             l1 = min(self.num_layers, l0 + step)
                             for l in range(l0, l1):
+                                if self.kv_queue is not None:
+                                    _take_token(self.kv_queue, f"post_events[{l}]")
                                 s.wait_event(post_events[l])
                             cache_ops.transfer_blocks(self.gpu_kv_caches, peer, table, layers=(l0, l1))
             return True
-        except _lib.LmsError as e:
+        except (_lib.LmsError, ValueError, TimeoutError) as e:
             print(f"Posting transfer failed. {e}")
             return False
 
@@ -521,25 +692,18 @@ class KVWorker:
         NVLink, into its own blocks ``block_ids``.  The kernel runs here, with plain loads from
         the mapped peer memory."""
         try:
-            desc = CacheDescriptor.deserialize(remote_descs)
             try:
-                pairs = build_push_pairs(block_ids, desc.block_ids)   # (local, remote)
-            except ValueError as e:
+                desc, pairs = self._transfer_table(remote_descs, block_ids)   # (local, remote)
+            except (ValueError, struct.error) as e:
                 print(f"Creating transfer failed. {e}")
                 return False
             with torch.cuda.device(self.device):
-                peer = self._peers.get(peer_name)
-                if peer is None:
-                    peer = PeerCache(desc)
-                    self._peers[peer_name] = peer
-                if peer.num_layers != self.num_layers or peer.chunk_bytes != self.chunk_bytes:
-                    print("Creating transfer failed. cache geometries differ")
-                    return False
+                peer = self._peer(peer_name, desc)
                 table = np.ascontiguousarray(pairs[:, ::-1])              # (remote src, local dst)
                 with torch.cuda.stream(stream or self.push_stream):
                     cache_ops.transfer_blocks(peer, self.gpu_kv_caches, table, pull=True)
             return True
-        except _lib.LmsError as e:
+        except (_lib.LmsError, ValueError) as e:
             print(f"Posting transfer failed. {e}")
             return False
 
@@ -547,6 +711,7 @@ class KVWorker:
         for p in self._peers.values():
             p.close()
         self._peers.clear()
+        self._staging.clear()
         if self._disk_threads is not None:
             self._disk_threads.shutdown(wait=True)
             self._disk_threads = None

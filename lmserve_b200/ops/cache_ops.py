@@ -24,10 +24,11 @@ import torch
 
 from .. import _lib
 
-try:  # C helpers for walking Python containers (csrc/packer.c); pure Python otherwise
+try:  # C helpers for walking Python containers (csrc/packer.c)
     from .. import _packer
-except ImportError:  # pragma: no cover - depends on the build
-    _packer = None
+except ImportError as e:  # a build without it would silently run the 4x slower Python loops
+    raise ImportError("lmserve_b200/_packer.so is missing: build it with "
+                      "`python -m lmserve_b200.build` (gcc, no CUDA needed)") from e
 
 PairList = Union[Sequence[Tuple[int, int]], np.ndarray, torch.Tensor]
 

@@ -27,10 +27,7 @@ import torch
 from . import _lib
 from .ops.cache_ops import _OnDevice, _stream_ptr
 
-try:  # the C packer (csrc/packer.c, built by lmserve_b200.build); pure-Python packing otherwise
-    from . import _packer
-except ImportError:  # pragma: no cover - depends on the build
-    _packer = None
+from .ops.cache_ops import _packer  # the C packer (csrc/packer.c); its absence is an ImportError
 
 MAX_BATCH = 4096  # LMS_STEP_MAX_BATCH
 

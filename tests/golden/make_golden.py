@@ -26,7 +26,7 @@ sys.path.insert(0, str(HERE.parent.parent))
 import numpy as np
 import torch
 
-from lmserve_b200 import workloads as W
+import workloads as W
 from oracle import triton_ref
 
 TORCH_DT = {"fp16": torch.float16, "bf16": torch.bfloat16}

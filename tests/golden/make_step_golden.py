@@ -15,7 +15,7 @@ import torch
 
 HERE = Path(__file__).resolve().parent
 sys.path.insert(0, str(HERE.parent.parent))
-from lmserve_b200 import workloads as W  # noqa: E402
+import workloads as W  # noqa: E402
 
 GENERATOR = dict(num_blocks=65536, block_size=16, num_decode=60, ctx_lo=1, ctx_hi=900, num_prefill=5,
                  chunk_tokens=128, max_offset=400, seed=9, spare_blocks=1)

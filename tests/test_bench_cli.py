@@ -44,7 +44,7 @@ def test_our_arm_refuses_to_run_without_a_gpu():
 
 
 def test_renumber_blocks_keeps_structure():
-    from lmserve_b200 import workloads as W
+    import workloads as W
     w = W.config2()
     new = bench.renumber_blocks(w.slot_mapping, 16, 2048, seed=3)
     assert new.max() < 2048 * 16 and len(np.unique(new)) == len(new)

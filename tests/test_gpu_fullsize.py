@@ -6,7 +6,8 @@ import numpy as np
 import pytest
 import torch
 
-from lmserve_b200 import _lib, workloads as W
+from lmserve_b200 import _lib
+import workloads as W
 from lmserve_b200.kv_worker import HostPool
 from lmserve_b200.ops import cache_ops
 

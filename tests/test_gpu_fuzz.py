@@ -5,7 +5,8 @@ import pytest
 import torch
 
 from helpers import to_tensor, to_words
-from lmserve_b200 import _lib, workloads as W
+from lmserve_b200 import _lib
+import workloads as W
 from lmserve_b200.kv_worker import HostPool
 from lmserve_b200.ops import cache_ops
 from oracle import cache_oracle

@@ -12,7 +12,8 @@ import pytest
 import torch
 
 from helpers import COPY_CASES, FILL_CASES, load_json, load_npz, sha, to_tensor, to_words
-from lmserve_b200 import _lib, workloads as W
+from lmserve_b200 import _lib
+import workloads as W
 from lmserve_b200.ops import cache_ops
 from oracle import cache_oracle
 

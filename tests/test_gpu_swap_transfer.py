@@ -8,7 +8,8 @@ import pytest
 import torch
 
 from helpers import to_tensor, to_words
-from lmserve_b200 import _lib, workloads as W
+from lmserve_b200 import _lib
+import workloads as W
 from lmserve_b200.kv_worker import BlockMapping, Device, HostPool, KVWorker
 from lmserve_b200.ops import cache_ops
 from oracle import cache_oracle
@@ -296,6 +297,119 @@ def test_kv_process_maps_the_model_process_cache_and_events():
     assert np.array_equal(to_words(gpu).reshape(gw.shape), gw)
 
 
+def _kv_process_late(params, in_pairs, out_pairs, delay, q):
+    """Child = the KV process of the waiter-first test: it fills host block 4 with a pattern,
+    lets `delay` seconds pass (the model process has issued its pre-hooks long before), swaps
+    the block in behind pre-events + tokens, and then at once asks for a swap-out that the
+    model's post-events and tokens release only later."""
+    try:
+        import time
+        import numpy as np
+        from lmserve_b200.kv_worker import Device, KVWorker
+        w = KVWorker.from_params("kv0", params)
+        L_ = w.num_layers
+        for l in range(L_):
+            w.host_pool.array.view(np.float16).reshape(w.host_pool.num_blocks, L_, -1)[4, l] = 5.0 + l
+        time.sleep(delay)
+        w.copy_kv([in_pairs], Device.Host, Device.GPU, pre_events=w.pre_events)
+        w.htod_stream.synchronize()
+        w.copy_kv([out_pairs], Device.GPU, Device.Host, post_events=w.post_events)
+        w.dtoh_stream.synchronize()
+        got = w.host_pool.array.view(np.float16).reshape(w.host_pool.num_blocks, L_, -1)[2, :, 0].tolist()
+        w.close()
+        q.put(("ok", got))
+    except Exception as e:  # pragma: no cover - reported to the parent
+        q.put(("error", repr(e)))
+
+
+def test_two_process_handshake_when_the_waiter_comes_first():
+    """The model process issues its pre-hooks BEFORE the KV process has recorded this step's
+    pre-events, and the KV process asks for its swap-out BEFORE the model has recorded the
+    post-events.  A stream wait binds to the last record issued so far (none here), so without
+    the token queues both sides would read stale blocks; with them the hook and the worker
+    hold their waits back until the other side's record has been issued."""
+    import time
+    from lmserve_b200.kv_worker import init_cache
+    L_, H, D, BS = 3, 2, 64, 16
+    per_block = L_ * 2 * BS * H * D * 2
+    kv, handle, params = init_cache(per_block * 12, per_block * 6, num_layers=L_, num_kv_heads=H,
+                                    head_dim=D, block_size=BS, dtype=torch.float16, device=DEV)
+    assert params.model_queue is not None and handle.kv_queue is params.kv_queue
+    kv.zero_()
+    torch.cuda.synchronize()
+
+    class Attention(torch.nn.Module):
+        def __init__(self, layer):
+            super().__init__()
+            self.layer = layer
+
+        def forward(self, x):
+            seen = kv[self.layer, 7].clone()
+            kv[self.layer, 3] = x + self.layer
+            return seen
+
+    layers = torch.nn.ModuleList(Attention(i) for i in range(L_))
+    handle.register_hooks(layers)
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    in_pairs = np.array([[4, 7]], dtype=np.int64)
+    out_pairs = np.array([[3, 2]], dtype=np.int64)
+    p = ctx.Process(target=_kv_process_late, args=(params, in_pairs, out_pairs, 1.0, q))
+    p.start()
+    x = torch.full((2, BS, H, D), 2.0, dtype=torch.float16, device=DEV)
+    handle.enable_wait_before_execute = True         # hooks run now; the child records in > 1 s
+    seen = [layer(x) for layer in layers]
+    torch.cuda.synchronize()
+    for l in range(L_):
+        assert (seen[l] == 5.0 + l).all(), "the layer read the block before it was swapped in"
+    handle.enable_wait_before_execute = False
+    time.sleep(0.5)                                  # the child is already waiting for post tokens
+    kv[:, 3] = 0
+    handle.enable_record_after_execute = True
+    for layer in layers:
+        layer(x)
+    status, payload = q.get(timeout=300)
+    p.join(timeout=60)
+    assert status == "ok", payload
+    assert payload == [2.0 + l for l in range(L_)]   # not the zeros that were there before
+
+
+def test_two_thread_handshake_with_the_worker_in_this_process():
+    """The same race with the KV worker on a second host thread of one process."""
+    import queue
+    import threading
+    import time
+    shape = W.SHAPES["llama31_8b_swap"].scaled(num_layers=4, num_blocks=16, num_kv_heads=2)
+    words, gpu = make_gpu_cache(shape, 97)
+    worker = KVWorker("kv0", gpu, num_host_blocks=4)
+    from lmserve_b200.kv_worker import KVWorkerHandle
+    try:
+        worker.model_queue, worker.kv_queue = queue.Queue(), queue.Queue()
+        pre = [torch.cuda.Event() for _ in range(4)]
+        handle = KVWorkerHandle(pre, [], model_queue=worker.model_queue, kv_queue=worker.kv_queue)
+        worker.host_pool.array[...] = 7
+        before = to_words(gpu).reshape(4, 16, -1)[:, 9].copy()
+
+        def kv_thread():
+            torch.cuda.set_device(gpu.device)
+            time.sleep(0.3)
+            worker.load_kv_blocks_from_host([np.array([[1, 9]])], pre_events=pre)
+
+        t = threading.Thread(target=kv_thread)
+        t.start()
+        got = []
+        for l in range(4):
+            handle.wait_before_layer(l)                  # blocks until the worker's token
+            got.append(gpu[l, 9].clone())
+        t.join()
+        torch.cuda.synchronize()
+        for l in range(4):
+            assert (to_words(got[l]).view(np.uint8) == 7).all()
+        assert not (before.view(np.uint8) == 7).all()
+    finally:
+        worker.close()
+
+
 def test_init_cache_and_layer_hooks_drive_the_swap_handshake():
     """init_cache sizes and allocates the cache as the reference does; the forward hooks record
     post_events after each attention layer has written its KV and make a layer wait for its
@@ -304,7 +418,8 @@ def test_init_cache_and_layer_hooks_drive_the_swap_handshake():
     L_, H, D, BS = 3, 2, 64, 16
     per_block = L_ * 2 * BS * H * D * 2
     kv, handle, params = init_cache(per_block * 12 + 100, per_block * 5, num_layers=L_, num_kv_heads=H,
-                                    head_dim=D, block_size=BS, dtype=torch.float16, device=DEV)
+                                    head_dim=D, block_size=BS, dtype=torch.float16, device=DEV,
+                                    mp_context=None)   # worker and model share this thread
     assert kv.shape == (L_, 12, 2, BS, H, D) and params.num_host_blocks == 5
     assert params.cache_shape == tuple(kv.shape) and len(params.pre_event_handles) == L_
     kv.zero_()
@@ -386,7 +501,7 @@ def _puller(desc_bytes, seed, local_blocks, q):
     try:
         import numpy as np
         from helpers import to_tensor, to_words
-        from lmserve_b200 import workloads as W
+        import workloads as W
         from lmserve_b200.kv_worker import KVWorker
         shape = W.SHAPES["llama31_70b_tp8"].scaled(num_layers=4, num_blocks=64)
         words = W.normal_words(np.random.default_rng(seed), shape.cache_shape, shape.dtype)
@@ -430,7 +545,7 @@ def _pusher(desc_bytes, seed, pairs_src, q, layered=False):
         import numpy as np
         import torch
         from helpers import to_tensor
-        from lmserve_b200 import workloads as W
+        import workloads as W
         from lmserve_b200.kv_worker import KVWorker
         shape = W.SHAPES["llama31_70b_tp8"].scaled(num_layers=4, num_blocks=64)
         words = W.normal_words(np.random.default_rng(seed), shape.cache_shape, shape.dtype)
@@ -476,6 +591,45 @@ def test_push_kv_from_another_process(layered):
     cache_oracle.transfer(src_words, want, np.stack([src_blocks, reserved[:4]], axis=1))
     assert np.array_equal(to_words(dst), want)
     decode.close()
+
+
+def test_push_and_pull_refuse_ids_and_descriptors_that_do_not_fit(capsys):
+    """Block ids outside either cache, a descriptor of another geometry and bytes that are no
+    descriptor are refused on the host with ``False`` and a printed reason; nothing is written
+    to the peer (the reference prints and returns False for a failed transfer,
+    ``kv_worker.py:396-409``)."""
+    from lmserve_b200.kv_worker import CacheDescriptor
+    shape = W.SHAPES["llama31_70b_tp8"].scaled(num_layers=3, num_blocks=32)
+    src_words, src = make_gpu_cache(shape, 87)
+    dst_words, dst = make_gpu_cache(shape.scaled(num_blocks=20), 88)
+    prefill, decode = KVWorker("p", src), KVWorker("d", dst)
+    try:
+        with pytest.raises(IndexError):
+            decode.get_descriptors([3, 20])                      # 20 is outside the 20-block cache
+        descs = decode.get_descriptors([3, 4, 5])
+        assert prefill.push_kv("d", descs, [1, 32]) is False      # local id out of range
+        assert prefill.push_kv("d", descs, [1, -1]) is False
+        assert prefill.push_kv("d", descs, [1, 2, 3, 4]) is False  # more blocks than reserved
+        forged = CacheDescriptor.deserialize(descs)
+        forged.block_ids = [3, 25]                                # remote id outside the peer cache
+        assert prefill.push_kv("d", forged.serialize(), [1, 2]) is False
+        assert decode.pull_kv("p", prefill.get_descriptors([0, 1]), [2, 20]) is False
+        other = CacheDescriptor.deserialize(descs)
+        other.chunk_bytes *= 2                                    # another geometry
+        assert prefill.push_kv("d", other.serialize(), [1]) is False
+        assert prefill.push_kv("d", b"not a descriptor", [1]) is False
+        out = capsys.readouterr().out
+        assert out.count("Creating transfer failed.") == 7
+        torch.cuda.synchronize()
+        assert np.array_equal(to_words(dst), dst_words) and np.array_equal(to_words(src), src_words)
+        assert prefill.push_kv("d", descs, [1, 2]) is True        # and a good one still works
+        prefill.push_stream.synchronize()
+        want = dst_words.copy()
+        cache_oracle.transfer(src_words, want, np.array([[1, 3], [2, 4]]))
+        assert np.array_equal(to_words(dst), want)
+    finally:
+        prefill.close()
+        decode.close()
 
 
 @pytest.mark.parametrize("variant", [0, 1, 2, 3, 4])

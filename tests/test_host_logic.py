@@ -4,7 +4,7 @@ import numpy as np
 import pytest
 import torch
 
-from lmserve_b200 import workloads as W
+import workloads as W
 from lmserve_b200.kv_worker import (BlockMapping, BlockMappingEntry, CacheDescriptor, Device,
                                     mappings_to_pairs)
 from lmserve_b200.ops import cache_ops
@@ -102,6 +102,83 @@ def test_descriptor_roundtrip():
     d = CacheDescriptor(b"\x01" * 64, 256, 3, 80, 1000, 1 << 23, 8192, 8192, [5, 9, 2])
     e = CacheDescriptor.deserialize(d.serialize())
     assert e == d
+    assert CacheDescriptor.deserialize(CacheDescriptor(b"\x02" * 64, 0, 0, 1, 1, 16, 16, 16, []).serialize()).block_ids == []
+
+
+def test_descriptor_rejects_anything_that_is_not_a_descriptor():
+    """The descriptor arrives over RPC: it is a fixed binary layout, and bytes that do not
+    fit it are refused (no object deserialization happens on the way)."""
+    import pickle
+    good = CacheDescriptor(b"\x01" * 64, 256, 3, 80, 1000, 1 << 23, 8192, 8192, [5, 9, 2]).serialize()
+    for bad in (b"", good[:40], good[:-1], good + b"\x00", b"XXXX" + good[4:],
+                pickle.dumps({"handle": b"x"}), good[:4] + b"\xff" * 8 + good[12:]):
+        with pytest.raises(ValueError):
+            CacheDescriptor.deserialize(bad)
+    with pytest.raises(ValueError):
+        CacheDescriptor(b"short", 0, 0, 1, 1, 16, 16, 16, []).serialize()
+
+
+class _FakeEvent:
+    def __init__(self, log, name):
+        self.log, self.name = log, name
+
+    def record(self, stream=None):
+        self.log.append(("record", self.name))
+
+
+class _FakeStream:
+    def __init__(self, log):
+        self.log = log
+
+    def wait_event(self, e):
+        self.log.append(("wait", e.name))
+
+
+def test_layer_handshake_waiter_issued_before_the_record():
+    """The model's pre-hook runs BEFORE the KV side has recorded this step's event (the order a
+    two-process deployment produces at will): the hook must hold its stream wait back until
+    the recorder's token arrives, because a stream wait binds to whatever record was issued
+    last.  Fake events and streams, two host threads."""
+    import queue
+    import threading
+    import time
+    from lmserve_b200.kv_worker import KVWorkerHandle
+    log = []
+    pre = [_FakeEvent(log, f"pre{i}") for i in range(3)]
+    post = [_FakeEvent(log, f"post{i}") for i in range(3)]
+    h = KVWorkerHandle(pre, post, model_queue=queue.Queue(), kv_queue=queue.Queue())
+    stream = _FakeStream(log)
+
+    def kv_side():
+        time.sleep(0.2)
+        for i in range(3):
+            pre[i].record()
+            h.model_queue.put(b"")
+            time.sleep(0.02)
+
+    t = threading.Thread(target=kv_side)
+    t.start()
+    for i in range(3):
+        h.wait_before_layer(i, stream)       # issued at once, long before the first record
+    t.join()
+    for i in range(3):
+        assert log.index(("record", f"pre{i}")) < log.index(("wait", f"pre{i}"))
+    # the other direction: the model records, then tells the KV side
+    log.clear()
+    for i in range(3):
+        h.record_after_layer(i, stream)
+    assert h.kv_queue.qsize() == 3 and [x for x in log] == [("record", f"post{i}") for i in range(3)]
+
+
+def test_layer_handshake_times_out_instead_of_hanging(monkeypatch):
+    import queue
+    from lmserve_b200 import kv_worker
+    monkeypatch.setattr(kv_worker, "HANDSHAKE_TIMEOUT_S", 0.05)
+    log = []
+    h = kv_worker.KVWorkerHandle([_FakeEvent(log, "pre0")], [], model_queue=queue.Queue())
+    with pytest.raises(TimeoutError, match="pre_events"):
+        h.wait_before_layer(0, _FakeStream(log))
+    assert log == []                             # no wait was issued on a stale event
 
 
 @pytest.mark.parametrize("cfg", ["config2", "config5_decode"])

@@ -101,7 +101,7 @@ def test_service_over_unix_socket_with_recording_worker():
 def test_service_end_to_end_on_gpu():
     """CopyKV GPU->Host then Host->GPU through the socket, with the real kernels."""
     from helpers import to_tensor, to_words
-    from lmserve_b200 import workloads as W
+    import workloads as W
     from lmserve_b200.kv_worker import KVWorker
     from oracle import cache_oracle
     shape = W.SHAPES["llama31_8b_swap"].scaled(num_layers=3, num_blocks=32, num_kv_heads=2)

@@ -10,7 +10,7 @@ import numpy as np
 import pytest
 import torch
 
-from lmserve_b200 import workloads as W
+import workloads as W
 from lmserve_b200.disagg import (Comm, build_push_pairs, kv_heads_per_rank, transfer_role)
 from lmserve_b200.kv_worker import CacheDescriptor
 

@@ -12,7 +12,7 @@ from hypothesis import given, settings, strategies as st
 
 from helpers import (COPY_CASES, FILL_CASES, GOLDEN, load_json, load_npz, sha, to_tensor,
                      to_words)
-from lmserve_b200 import workloads as W
+import workloads as W
 from oracle import cache_oracle, torch_ref, triton_ref
 
 
@@ -147,7 +147,7 @@ def test_golden_regenerates_from_reference(tmp_path):
     code = (
         "import os, sys, json; os.environ['TRITON_INTERPRET']='1'; sys.path.insert(0, %r);"
         "import numpy as np, torch;"
-        "from lmserve_b200 import workloads as W; from oracle import triton_ref;"
+        "import workloads as W; from oracle import triton_ref;"
         "import hashlib;"
         "c=W.config1(); p=W.plumbing_payload(c);"
         "t=torch.from_numpy(p['kv_caches'].view(np.int16).copy()).view(torch.float16);"

@@ -7,7 +7,8 @@ import pytest
 import torch
 
 from helpers import load_npz, to_tensor, to_words
-from lmserve_b200 import _lib, workloads as W
+from lmserve_b200 import _lib
+import workloads as W
 from oracle import cache_oracle, rope_oracle
 
 ROPE_CASES = ["rope_fp16_llama", "rope_fp16_d64"]

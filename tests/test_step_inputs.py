@@ -7,7 +7,8 @@ import numpy as np
 import pytest
 import torch
 
-from lmserve_b200 import _lib, workloads as W
+from lmserve_b200 import _lib
+import workloads as W
 from lmserve_b200.step_inputs import InferInput, pack_requests
 from oracle import step_oracle
 

@@ -6,7 +6,7 @@ import torch
 
 from helpers import to_tensor, to_words
 import lmserve_b200.torch_ops as T
-from lmserve_b200 import workloads as W
+import workloads as W
 from oracle import cache_oracle
 
 DEV = "cuda:0"

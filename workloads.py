@@ -286,9 +286,13 @@ def make_transfer(shape: KVShape, num_seqs: int, tokens_per_seq: int, seed: int,
 
 
 def transfer_peer(rank: int, world: int) -> Tuple[str, Optional[int]]:
-    """Role and partner of `rank` in the disaggregated pairing (see ``disagg.transfer_role``)."""
-    from .disagg import transfer_role
-    return transfer_role(rank, world)
+    """Role and partner of `rank` in the disaggregated pairing: prefill rank g sends to decode
+    rank g + world / 2 (the pairing ``lmserve_b200.disagg.transfer_role`` gives the product;
+    restated here so that the input generator does not import the product package)."""
+    if world < 2 or world % 2 or not (0 <= rank < world):
+        return "none", None
+    half = world // 2
+    return ("prefill", rank + half) if rank < half else ("decode", rank - half)
 
 
 # ------------------------------------------------------------------ presets
