@@ -39,8 +39,12 @@ TUNE_WRITE_VPT = 9
 TUNE_SWAP_VARIANT = 10
 TUNE_WRITE_PDL = 11
 TUNE_SWAP_ENGINE = 12
+TUNE_WRITE_PREFETCH = 13
+TUNE_STAGED_STREAMS = 14
+TUNE_COUNT = 15
 
-# name -> (restype, argtypes); one entry per declaration in include/lmserve_kv.h
+# name -> (restype, argtypes); one entry per declaration in include/lmserve_kv.h and
+# include/lmserve_kv_bench.h
 SIGNATURES = {
     "lms_version": (c_int, []),
     "lms_strerror": (c_char_p, [c_int]),
@@ -50,6 +54,8 @@ SIGNATURES = {
     "lms_get_tuning": (c_int, [c_int]),
     "lms_set_debug_checks": (c_int, [c_int]),
     "lms_check_device_errors": (c_int, [c_void_p, POINTER(c_int64), POINTER(c_int64)]),
+    "lms_error_record_async": (c_int, [c_void_p, c_void_p]),
+    "lms_write_kernel_name": (c_char_p, [c_int64, c_int64]),
     "lms_reshape_and_cache": (c_int, [
         c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_int64, c_int64,
         c_void_p, c_int64, c_int64, c_int32, c_int64, c_void_p]),

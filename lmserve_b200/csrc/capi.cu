@@ -11,6 +11,7 @@
 #include <string.h>
 
 #include "../../include/lmserve_kv.h"
+#include "../../include/lmserve_kv_bench.h"
 #include "kernels.cuh"
 
 // A validated cache write (see lms_write_plan_create).
@@ -39,10 +40,11 @@ struct DeviceState {
   // large DMA transfers run on and the events that hand the two halves of the caller's
   // staging buffer back and forth between that stream and the caller's stream.
   struct Staged {
-    cudaStream_t copy = nullptr;
+    cudaStream_t copy[2] = {nullptr, nullptr};  // transfers alternate between the two
     cudaEvent_t ready[2] = {nullptr, nullptr};  // half b holds data for the consumer
     cudaEvent_t freed[2] = {nullptr, nullptr};  // half b has been consumed
     cudaEvent_t start = nullptr;
+    cudaEvent_t join = nullptr;                 // second copy stream has finished a group
     std::mutex mutex;
   } staged[2];
 };
@@ -193,6 +195,7 @@ int write_launch(WriteParams p, void* stream) {
   const int tile = tuned(LMS_TUNE_WRITE_TILE_BYTES, 0);
   const int vpt = tuned(LMS_TUNE_WRITE_VPT, 2);
   const bool pdl = tuned(LMS_TUNE_WRITE_PDL, 1) == 1;
+  p.prefetch = tuned(LMS_TUNE_WRITE_PREFETCH, 1) == 1 ? 1 : 0;
   LMS_CUDA(launch_write(p, variant, tile, vpt, ds->sms, pdl, (cudaStream_t)stream));
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return LMS_OK;
@@ -430,6 +433,20 @@ int lms_check_device_errors(void* stream, int64_t* index, int64_t* value) {
     return LMS_ERR_CUDA;
   }
   return LMS_ERR_INDEX;
+}
+
+int lms_error_record_async(void* host_dst32, void* stream) {
+  if (!host_dst32) return LMS_ERR_NULL;
+  DeviceState* ds = nullptr;
+  if (int rc = device_state(&ds)) return rc;
+  static_assert(sizeof(ErrRecord) == 32, "the error record is 32 bytes");
+  LMS_CUDA(cudaMemcpyAsync(host_dst32, ds->err.load(std::memory_order_relaxed), sizeof(ErrRecord),
+                           cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+  return LMS_OK;
+}
+
+const char* lms_write_kernel_name(int64_t row_bytes, int64_t total_bytes) {
+  return write_kernel_name(tuned_variant(LMS_TUNE_WRITE_VARIANT, -1), row_bytes, total_bytes);
 }
 
 int lms_reshape_and_cache(const void* key, const void* value,
@@ -878,13 +895,14 @@ int swap_blocks_dma(int direction, char* gpu, int64_t gpu_layer_stride,
 // or of runs of adjacent host blocks - which use the link's large packets.  The two halves
 // alternate, so the DMA of one group overlaps the gather / scatter of the next.
 int staged_setup(DeviceState::Staged& st) {
-  if (st.copy != nullptr) return LMS_OK;
-  LMS_CUDA(cudaStreamCreateWithFlags(&st.copy, cudaStreamNonBlocking));
+  if (st.join != nullptr) return LMS_OK;
   for (int b = 0; b < 2; ++b) {
+    LMS_CUDA(cudaStreamCreateWithFlags(&st.copy[b], cudaStreamNonBlocking));
     LMS_CUDA(cudaEventCreateWithFlags(&st.ready[b], cudaEventDisableTiming));
     LMS_CUDA(cudaEventCreateWithFlags(&st.freed[b], cudaEventDisableTiming));
   }
   LMS_CUDA(cudaEventCreateWithFlags(&st.start, cudaEventDisableTiming));
+  LMS_CUDA(cudaEventCreateWithFlags(&st.join, cudaEventDisableTiming));
   return LMS_OK;
 }
 
@@ -947,18 +965,26 @@ int swap_blocks_staged(int direction, char* gpu, int64_t gpu_layer_stride,
   const int64_t n_groups = (n_pairs + group - 1) / group;
   const int ctas = ds->sms * 2;
 
+  // One transfer per host block leaves the link idle between transfers on a single stream
+  // (about 3 us per 2 MiB block); alternating between two copy streams fills the gaps.
+  const int n_copy = tuned(LMS_TUNE_STAGED_STREAMS, 2) >= 2 ? 2 : 1;
+  cudaStream_t c0 = st.copy[0], c1 = st.copy[n_copy - 1];
+
   return with_host_table(table.data(), n_pairs, stream, [&](const int64_t* dev_table) {
     if (!out) {
       // the DMA reads host memory that earlier work of the caller's stream may still write
       LMS_CUDA(cudaEventRecord(st.start, stream));
-      LMS_CUDA(cudaStreamWaitEvent(st.copy, st.start, 0));
+      LMS_CUDA(cudaStreamWaitEvent(c0, st.start, 0));
+      if (n_copy == 2) LMS_CUDA(cudaStreamWaitEvent(c1, st.start, 0));
     }
     for (int64_t g = 0; g < n_groups; ++g) {
       const int b = (int)(g & 1);
       const int64_t first = g * group;
       const int64_t count = std::min(group, n_pairs - first);
       char* buf = staging + (int64_t)b * half;
+      // the transfers of one group, spread over the copy streams; c0 ends up behind both
       auto dma = [&]() -> int {
+        int turn = 0;
         for (int64_t k = 0; k < count;) {
           int64_t len = 1;
           if (runs)
@@ -967,11 +993,16 @@ int swap_blocks_staged(int direction, char* gpu, int64_t gpu_layer_stride,
               ++len;
           char* h = hbase + order[(size_t)(first + k)].first * host_block_stride;
           char* d = buf + k * per_block;
+          cudaStream_t cs = (turn++ & 1) ? c1 : c0;
           if (out)
-            LMS_CUDA(cudaMemcpyAsync(h, d, (size_t)(len * per_block), cudaMemcpyDeviceToHost, st.copy));
+            LMS_CUDA(cudaMemcpyAsync(h, d, (size_t)(len * per_block), cudaMemcpyDeviceToHost, cs));
           else
-            LMS_CUDA(cudaMemcpyAsync(d, h, (size_t)(len * per_block), cudaMemcpyHostToDevice, st.copy));
+            LMS_CUDA(cudaMemcpyAsync(d, h, (size_t)(len * per_block), cudaMemcpyHostToDevice, cs));
           k += len;
+        }
+        if (n_copy == 2) {
+          LMS_CUDA(cudaEventRecord(st.join, c1));
+          LMS_CUDA(cudaStreamWaitEvent(c0, st.join, 0));
         }
         return LMS_OK;
       };
@@ -990,13 +1021,17 @@ int swap_blocks_staged(int direction, char* gpu, int64_t gpu_layer_stride,
         if (g >= 2) LMS_CUDA(cudaStreamWaitEvent(stream, st.freed[b], 0));
         if (int rc = kernel()) return rc;
         LMS_CUDA(cudaEventRecord(st.ready[b], stream));
-        LMS_CUDA(cudaStreamWaitEvent(st.copy, st.ready[b], 0));
+        LMS_CUDA(cudaStreamWaitEvent(c0, st.ready[b], 0));
+        if (n_copy == 2) LMS_CUDA(cudaStreamWaitEvent(c1, st.ready[b], 0));
         if (int rc = dma()) return rc;
-        LMS_CUDA(cudaEventRecord(st.freed[b], st.copy));
+        LMS_CUDA(cudaEventRecord(st.freed[b], c0));
       } else {
-        if (g >= 2) LMS_CUDA(cudaStreamWaitEvent(st.copy, st.freed[b], 0));
+        if (g >= 2) {
+          LMS_CUDA(cudaStreamWaitEvent(c0, st.freed[b], 0));
+          if (n_copy == 2) LMS_CUDA(cudaStreamWaitEvent(c1, st.freed[b], 0));
+        }
         if (int rc = dma()) return rc;
-        LMS_CUDA(cudaEventRecord(st.ready[b], st.copy));
+        LMS_CUDA(cudaEventRecord(st.ready[b], c0));
         LMS_CUDA(cudaStreamWaitEvent(stream, st.ready[b], 0));
         if (int rc = kernel()) return rc;
         LMS_CUDA(cudaEventRecord(st.freed[b], stream));

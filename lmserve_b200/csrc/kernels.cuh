@@ -55,6 +55,7 @@ struct WriteParams {
   int pieces_per_row;
   ErrRecord* err;
   int checks;
+  int prefetch;         // untiled kernels: prefetch the source lines into L2 before the launch wait
 };
 
 // variant: 0 = 16-byte vectors, 1 = 32-byte vectors, 2 = bulk copies;
@@ -62,6 +63,8 @@ struct WriteParams {
 // pdl: launch the untiled kernel with programmatic stream serialization
 cudaError_t launch_write(const WriteParams& p, int variant, int tile_bytes,
                          int vpt, int sms, bool pdl, cudaStream_t stream);
+// Name of the kernel launch_write would run for this geometry under `variant` (-1 = built-in).
+const char* write_kernel_name(int variant, long long row_bytes, long long total_bytes);
 
 // ------------------------------------------------------------ chunk copies
 // One kernel family serves copy_blocks, swap-out, swap-in and transfer: every

@@ -20,6 +20,7 @@ struct ErrRecord {
   unsigned int where;  // kernel id
   long long index;     // position in the index table
   long long value;     // offending value
+  long long reserved;  // pads the record to 32 bytes
 };
 
 enum : unsigned int {
@@ -54,6 +55,13 @@ __device__ __forceinline__ uint64_t policy_evict_last() {
   uint64_t p;
   asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
   return p;
+}
+
+// A hint that brings the 128-byte line of `p` into L2.  It returns nothing and orders nothing,
+// so it may be issued for memory another kernel is still writing: L2 is the point of coherence,
+// a later load sees whatever was written last.
+__device__ __forceinline__ void prefetch_l2(const void* p) {
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
 }
 
 // ---------------------------------------------------------------- 16-byte path

@@ -217,14 +217,21 @@ write_rows_direct(const WriteParams p, const int row_vecs, const int row_shift,
     layer = (int)(q / p.num_tokens);
     t = (int)(q - (long long)layer * p.num_tokens);
   }
+  const char* src = (kv ? p.value + (long long)layer * p.val_layer + (long long)t * p.val_tok
+                        : p.key + (long long)layer * p.key_layer + (long long)t * p.key_tok) +
+                    (long long)c * Vec::kBytes;
+  // Hints only (see prefetch_l2): the source line and the slot line start their way from DRAM
+  // while the previous kernel of the stream is still draining.
+  if (p.prefetch && v < n_vec_total) {
+    if ((c & (128 / Vec::kBytes - 1)) == 0) prefetch_l2(src);
+    if (c == 0 && kv == 0 && (t & 15) == 0 && p.slots != nullptr)
+      prefetch_l2(p.slots + (long long)layer * p.slot_layer + t);
+  }
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (v >= n_vec_total) return;
 
   const SlotRaw raw = slot_fetch_begin(p, layer, t);
-  const char* src = (kv ? p.value + (long long)layer * p.val_layer + (long long)t * p.val_tok
-                        : p.key + (long long)layer * p.key_layer + (long long)t * p.key_tok) +
-                    (long long)c * Vec::kBytes;
   Vec r;
   ld(r, src);
   const long long off =
@@ -268,6 +275,16 @@ write_rows_pair(const WriteParams p, const int row_vecs, const int row_shift,
   char* kout = p.kcache + (long long)layer * p.cache_layer;
   char* vout = p.vcache + (long long)layer * p.cache_layer;
 
+  if (p.prefetch) {
+#pragma unroll
+    for (int j = 0; j < TOK; ++j)
+      if (t[j] >= 0 && (c[j] & (128 / Vec::kBytes - 1)) == 0) {
+        prefetch_l2(kin + (long long)t[j] * p.key_tok + (long long)c[j] * Vec::kBytes);
+        prefetch_l2(vin + (long long)t[j] * p.val_tok + (long long)c[j] * Vec::kBytes);
+        if (c[j] == 0 && (t[j] & 15) == 0 && p.slots != nullptr)
+          prefetch_l2(p.slots + (long long)layer * p.slot_layer + t[j]);
+      }
+  }
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
@@ -354,7 +371,19 @@ write_rows_pair_persistent(const WriteParams p, const int row_vecs, const int ro
 
   Tile a, b;
   int tile = blockIdx.x;
-  if (tile < n_tiles) locate(a, tile);
+  if (tile < n_tiles) {
+    locate(a, tile);
+    if (p.prefetch) {
+      const char* kin = p.key + (long long)a.layer * p.key_layer;
+      const char* vin = p.value + (long long)a.layer * p.val_layer;
+#pragma unroll
+      for (int j = 0; j < TOK; ++j)
+        if (a.t[j] >= 0 && (a.c[j] & (128 / Vec::kBytes - 1)) == 0) {
+          prefetch_l2(kin + (long long)a.t[j] * p.key_tok + (long long)a.c[j] * Vec::kBytes);
+          prefetch_l2(vin + (long long)a.t[j] * p.val_tok + (long long)a.c[j] * Vec::kBytes);
+        }
+    }
+  }
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (tile >= n_tiles) return;
@@ -640,6 +669,20 @@ cudaError_t launch_vec_vpt(const WriteParams& p, int tile_bytes, int vpt, int sm
 }
 
 }  // namespace
+
+const char* write_kernel_name(int variant, long long row_bytes, long long total_bytes) {
+  const bool a32 = (row_bytes & 31) == 0;
+  if (variant < 0) variant = a32 ? 3 : (total_bytes <= (16ll << 20) ? 4 : 0);
+  switch (variant) {
+    case 0: case 1: return "write_rows_vec";
+    case 2: return "write_rows_bulk";
+    case 3: case 4: return "write_rows_direct";
+    case 5: return "write_rows_pair";
+    case 6: return "write_rows_multi";
+    case 7: return "write_rows_pair_persistent";
+    default: return "unknown";
+  }
+}
 
 cudaError_t launch_write(const WriteParams& p_in, int variant, int tile_bytes,
                          int vpt, int sms, bool pdl, cudaStream_t stream) {

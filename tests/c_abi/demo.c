@@ -12,6 +12,7 @@
 #include <string.h>
 
 #include "lmserve_kv.h"
+#include "lmserve_kv_bench.h"
 
 #define CHECK_CUDA(x) do { cudaError_t e_ = (x); if (e_ != cudaSuccess) { \
   fprintf(stderr, "%s: %s\n", #x, cudaGetErrorString(e_)); return 2; } } while (0)

@@ -8,12 +8,24 @@ import pytest
 
 from lmserve_b200 import _lib
 
-HEADER = Path(__file__).resolve().parent.parent / "include" / "lmserve_kv.h"
+INCLUDE = Path(__file__).resolve().parent.parent / "include"
+HEADER = INCLUDE / "lmserve_kv.h"              # the drop-in boundary
+BENCH_HEADER = INCLUDE / "lmserve_kv_bench.h"  # measurement / test instruments
 
 
-def declared_functions():
-    text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
-    return sorted(set(re.findall(r"\b(lms_[a-z0-9_]+)\s*\(", text)))
+def declared_functions(headers=(HEADER, BENCH_HEADER)):
+    names = set()
+    for h in headers:
+        text = re.sub(r"/\*.*?\*/", "", h.read_text(), flags=re.S)
+        names |= set(re.findall(r"\b(lms_[a-z0-9_]+)\s*\(", text))
+    return sorted(names)
+
+
+def test_the_product_header_carries_no_bench_hooks():
+    product = declared_functions((HEADER,))
+    for hook in ("lms_set_tuning", "lms_launch_count", "lms_memcpy_async", "lms_selftest_bounded_wait"):
+        assert hook not in product
+    assert "LMS_TUNE_" not in re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
 
 
 def test_header_declares_the_path():

@@ -18,7 +18,7 @@ DEV = "cuda:0"
 @pytest.fixture(autouse=True)
 def _reset_tuning():
     yield
-    for key in range(1, 13):
+    for key in range(1, _lib.TUNE_COUNT):
         _lib.lib().lms_set_tuning(key, -1)
 
 
