@@ -24,6 +24,33 @@ def test_reference_arm_prints_one_json_line():
     assert d["cpu_baseline"]["kind"] == "port" and d["cpu_baseline"]["cores"] >= 1
     assert d["e2e"] == {"value": d["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
     assert d["config"]["bytes_per_step"] == 64 << 20 and d["value"] > 0
+    # both arms describe the workload with the very same dictionary
+    assert d["config"] == bench.headline_config()
+    assert d["run"]["timing"]["rounds"] >= 3 and d["run"]["timing"]["steps_per_round"] == 2
+
+
+def test_reference_arm_does_not_load_the_product_library():
+    """The CPU arm times the oracle port; it must not map the product's shared objects."""
+    code = ("import sys; sys.argv=['bench.py','--impl','reference','--steps','1','--warmup','3'];"
+            "import runpy; runpy.run_path(%r, run_name='__main__');"
+            "maps=open('/proc/self/maps').read();"
+            "assert 'liblmserve_kv' not in maps and '_packer' not in maps, 'product .so mapped';"
+            "assert 'lmserve_b200' not in sys.modules") % str(ROOT / "bench.py")
+    out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300, cwd=ROOT)
+    assert out.returncode == 0, out.stderr[-2000:]
+
+
+def test_steps_per_graph_divides_the_step_count():
+    assert bench.steps_per_graph(20) == 20 and bench.steps_per_graph(1) == 1
+    assert bench.steps_per_graph(200) == 50 and 200 % bench.steps_per_graph(200) == 0
+    assert bench.steps_per_graph(64) == 64 and bench.steps_per_graph(128) == 64
+    assert bench.steps_per_graph(127) == 40      # a prime above the cap: remainder launched eagerly
+
+
+def test_profile_traffic_follows_the_kernel():
+    val, src = bench.profile_traffic("write_rows_direct")
+    assert val is None or (val > 1e6 and src.startswith("write_rows_direct"))
+    assert bench.profile_traffic("no_such_kernel") == (None, None)
 
 
 def test_reference_arm_other_ranks_stay_silent():
@@ -62,7 +89,13 @@ def test_host_pool_blocks_respects_the_cap():
     assert n * per_block <= 1 << 30 and n >= 1 and (n & (n - 1)) == 0
 
 
-def test_compact_decode_case_is_the_same_step():
-    w, shape, slots = bench.compact_decode_case()
-    assert shape.num_blocks == len(np.unique(w.slot_mapping // 16))
-    assert np.array_equal(slots % 16, w.slot_mapping % 16) and len(np.unique(slots)) == 256
+def test_compact_decode_cases_are_the_same_steps():
+    import workloads as W
+    w, shape, slots = bench.compact_decode_cases(3)
+    originals = [W.config2(seed=1002 + 17 * i).slot_mapping for i in range(3)]
+    assert shape.num_blocks == len(np.unique(np.concatenate(originals) // 16))
+    for got, want in zip(slots, originals):
+        assert np.array_equal(got % 16, want % 16) and len(np.unique(got)) == 256
+        assert got.max() < shape.num_blocks * 16
+        # tokens that shared a block still share one
+        assert len(set(zip((want // 16).tolist(), (got // 16).tolist()))) == len(np.unique(want // 16))
