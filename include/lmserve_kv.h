@@ -349,8 +349,10 @@ int lms_transfer_blocks(const void* src, int64_t src_layer_stride,
  * (runtime/worker/llm_worker/ops/cache_ops.py:12-19) and the swap / push paths walk
  * protobuf BlockMapping entries on the host (runtime/worker/llm_worker/kv_worker.py:204-211,
  * 220-227,375-387).  The table is uploaded on `stream` into a per-device table buffer owned
- * by the library (cudaMalloc, grown on demand, so do not make a call that has to grow it
- * inside stream capture), then the same kernel runs.  Calls on different streams are ordered
+ * by the library (cudaMalloc, grown on demand), then the same kernel runs.  These entry points
+ * cannot be captured into a CUDA graph - a replay would upload from a host buffer the caller
+ * has long reused - and return LMS_ERR_UNSUPPORTED when `stream` is capturing: upload the
+ * table yourself and capture the device-table entry point.  Calls on different streams are ordered
  * against each other through an event so that the shared buffer is never overwritten while a
  * kernel still reads it.  `host_pairs` may be reused as soon as the call returns when it is
  * pageable memory; page-locked memory must stay valid until `stream` has passed the call.

@@ -158,6 +158,8 @@ def check(status: int) -> None:
         return
     handle = lib()
     msg = handle.lms_strerror(status).decode()
-    if status == LMS_ERR_CUDA:
-        msg += ": " + handle.lms_last_cuda_error().decode()
+    if status in (LMS_ERR_CUDA, LMS_ERR_UNSUPPORTED, LMS_ERR_INDEX):
+        detail = handle.lms_last_cuda_error().decode()
+        if detail:
+            msg += ": " + detail
     raise LmsError(status, msg)

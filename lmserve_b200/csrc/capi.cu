@@ -293,12 +293,30 @@ int table_release(DeviceState* ds, cudaStream_t stream) {
   return LMS_OK;
 }
 
+// The entry points that upload a host-side table cannot be captured into a CUDA graph: the
+// upload would be replayed from a host buffer the caller has long reused, and the shared
+// table is guarded by an event recorded outside the capture.  They say so instead of failing
+// somewhere inside the runtime.
+int refuse_capture(cudaStream_t stream) {
+  cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(stream, &st) != cudaSuccess) {
+    cudaGetLastError();
+    return LMS_OK;  // let the real call report whatever is wrong with the stream
+  }
+  if (st == cudaStreamCaptureStatusNone) return LMS_OK;
+  snprintf(g_cuda_msg, sizeof(g_cuda_msg),
+           "a host-side pair table cannot be used while the stream is being captured; upload "
+           "the table yourself and call the device-table entry point");
+  return LMS_ERR_UNSUPPORTED;
+}
+
 // Runs `launch(device_pairs)` with the host table uploaded first.
 template <class F>
 int with_host_table(const int64_t* host_pairs, int64_t n_pairs, void* stream, F launch) {
   if (n_pairs < 0) return LMS_ERR_RANGE;
   if (n_pairs == 0) return launch((const int64_t*)nullptr);
   if (!host_pairs) return LMS_ERR_NULL;
+  if (int rc = refuse_capture((cudaStream_t)stream)) return rc;
   DeviceState* ds = nullptr;
   if (int rc = device_state(&ds)) return rc;
   std::lock_guard<std::mutex> lock(ds->table_mutex);

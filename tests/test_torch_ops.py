@@ -64,7 +64,7 @@ def test_writes_and_copy_match_the_oracle_eager_and_in_a_cuda_graph():
     torch.cuda.synchronize()
     assert np.array_equal(to_words(got), want)
 
-    # layer by layer, host-side pair table, replayed from a graph
+    # layer by layer, pair table on the device, replayed from a graph
     got2 = to_tensor(cache, "bf16", DEV)
     ops.reshape_and_cache(k[0], v[0], got2[0], s)       # first call outside the capture
     got2.copy_(to_tensor(cache, "bf16", DEV))
@@ -77,6 +77,19 @@ def test_writes_and_copy_match_the_oracle_eager_and_in_a_cuda_graph():
     g.replay()
     torch.cuda.synchronize()
     assert np.array_equal(to_words(got2), want)
+
+    # a HOST-side pair table cannot be captured (a replay would re-read the caller's buffer):
+    # the library says so instead of failing inside the runtime, and the capture stays usable
+    from lmserve_b200 import _lib
+    from lmserve_b200.ops import cache_ops
+    g2 = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g2):
+        with pytest.raises(_lib.LmsError) as e:
+            cache_ops.copy_blocks(got2, pairs)
+        assert e.value.status == _lib.LMS_ERR_UNSUPPORTED and "captured" in str(e.value)
+        ops.reshape_and_cache(k[0], v[0], got2[0], s)
+    g2.replay()
+    torch.cuda.synchronize()
 
 
 @pytest.mark.gpu

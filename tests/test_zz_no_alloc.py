@@ -84,3 +84,55 @@ def test_static_table_entry_point_limits_and_argument_errors():
     assert _run(f, kv2, pairs, False) == _lib.LMS_OK
     torch.cuda.synchronize()
     assert torch.equal(kv2[:, 20000:20000 + n], kv2[:, :n])
+
+
+_FRESH_PROCESS = r"""
+import sys, json
+sys.path.insert(0, {root!r})
+import numpy as np, torch
+from lmserve_b200 import _lib
+torch.cuda.set_device(0)
+lib = _lib.lib()
+kv = torch.arange(2 * 40000 * 8, dtype=torch.int16, device="cuda:0").view(2, 40000, 8)
+stream = torch.cuda.current_stream().cuda_stream
+torch.cuda.synchronize()
+
+def call(n):
+    pairs = np.stack([np.arange(n), 20000 + np.arange(n)], axis=1).astype(np.int64)
+    before = lib.lms_launch_count()
+    rc = lib.lms_copy_blocks_host_static(kv.data_ptr(), 40000 * 16, 16, 16, 2, pairs.ctypes.data, n, stream)
+    torch.cuda.synchronize()
+    return rc, lib.lms_launch_count() - before, torch.cuda.mem_get_info(0)[0]
+
+free0 = torch.cuda.mem_get_info(0)[0]
+out = dict(free0=free0, calls=[call(64), call(5), call(16384), call(64)])
+out["ok"] = bool(torch.equal(kv[:, 20000:20000 + 16384], kv[:, :16384]))
+print(json.dumps(out))
+"""
+
+
+def test_static_table_entry_point_allocates_nothing_in_a_fresh_process():
+    """The property the entry point exists for, checked where nothing else has run: a child
+    process makes its very first call into the library through ``lms_copy_blocks_host_static``
+    (no ``lms_init_device``, no other ``*_host`` call before it, so no error record and no
+    upload table exist), then calls it again with a short, the longest possible and a short
+    table.  Free device memory (``cudaMemGetInfo``) must not move from the first call's level —
+    the largest table included, where a growing buffer would have to be allocated — and every
+    call must launch exactly one kernel.  The first call itself may lower the level once: the
+    driver loads the library's code image, which contains the 256 KiB table, on first use."""
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+    root = str(Path(__file__).resolve().parent.parent)
+    out = subprocess.run([sys.executable, "-c", _FRESH_PROCESS.format(root=root)], capture_output=True,
+                         text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-2000:]
+    d = json.loads(out.stdout.strip().splitlines()[-1])
+    assert d["ok"]
+    (rc1, n1, f1), rest = d["calls"][0], d["calls"][1:]
+    assert rc1 == _lib.LMS_OK and n1 == 1
+    assert 0 <= d["free0"] - f1 <= 64 << 20, "the first call took more than a code image from the device"
+    for rc, launches, free in rest:
+        assert rc == _lib.LMS_OK and launches == 1
+        assert free == f1, "a later call changed the amount of free device memory"
