@@ -47,8 +47,8 @@ extern "C" {
 #define LMS_TUNE_WRITE_PREFETCH 13 /* 1 (built-in) = the untiled cache-write kernels prefetch their source
                                      lines into L2 before the programmatic-launch wait (a hint: it
                                      cannot change a result); 2 = off */
-#define LMS_TUNE_STAGED_STREAMS 14 /* copy streams lms_swap_blocks_staged spreads its transfers over: 1 or
-                                      2 (built-in) */
+#define LMS_TUNE_STAGED_STREAMS 14 /* copy streams lms_swap_blocks_staged spreads its transfers over: 1
+                                      (built-in) or 2 */
 #define LMS_TUNE__COUNT 15
 
 /* Overrides a launch tunable for every later call in this process. */

@@ -58,7 +58,24 @@ def pcie_link(device_index: int, sysfs: str = "/sys/bus/pci/devices") -> Dict[st
     for key in ("current_link_speed", "current_link_width", "max_link_speed", "max_link_width",
                 "numa_node", "local_cpulist"):
         out[key] = _read(base / key)
+    if out["current_link_speed"] is None:
+        out.update(_nvml_link(device_index))     # containers often hide the sysfs attributes
     return out
+
+
+def _nvml_link(device_index: int) -> Dict[str, Optional[str]]:
+    """The same link facts through NVML queries (read-only), where sysfs does not show them."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(device_index)
+        return {"current_link_gen": str(pynvml.nvmlDeviceGetCurrPcieLinkGeneration(h)),
+                "current_link_width": str(pynvml.nvmlDeviceGetCurrPcieLinkWidth(h)),
+                "max_link_gen": str(pynvml.nvmlDeviceGetMaxPcieLinkGeneration(h)),
+                "max_link_width": str(pynvml.nvmlDeviceGetMaxPcieLinkWidth(h)),
+                "source": "nvml"}
+    except Exception:  # noqa: BLE001 - no NVML, no answer
+        return {}
 
 
 def local_cpus(device_index: int, sysfs: str = "/sys/bus/pci/devices") -> Optional[List[int]]:

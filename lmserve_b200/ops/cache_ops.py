@@ -335,6 +335,8 @@ class PagedWritePlan:
 
 _PAGED_PLANS: Dict[tuple, PagedWritePlan] = {}
 _PAGED_PLANS_MAX = 2048
+_INDEX_ARGS: tuple = (None, None, None, None)   # the index tensors of the previous call ...
+_INDEX_KEY: tuple = ()                          # ... and their part of the plan key
 
 
 def append_paged_kv_cache(
@@ -364,23 +366,35 @@ def append_paged_kv_cache(
     a :class:`PagedWritePlan` keyed on everything the validation looked at (addresses, shapes,
     strides, dtypes); a repeat call is a dictionary lookup and one C call.
     """
-    tensor_cache = type(paged_kv_cache) is torch.Tensor
-    if tensor_cache:
-        c0, c1 = paged_kv_cache, paged_kv_cache
+    # Two-part key.  The four index tensors are the same Python objects for every layer of a
+    # step (``input_params.*`` in LMServe), so their part of the key is recomputed only when
+    # one of the objects changes; the per-layer part reads what differs from layer to layer.
+    global _INDEX_ARGS, _INDEX_KEY
+    if (_INDEX_ARGS[0] is batch_indices and _INDEX_ARGS[1] is positions
+            and _INDEX_ARGS[2] is kv_indices and _INDEX_ARGS[3] is kv_indptr):
+        index_key = _INDEX_KEY
+    else:
+        index_key = (batch_indices.data_ptr(), positions.data_ptr(), kv_indices.data_ptr(),
+                     kv_indptr.data_ptr(), batch_indices.dtype, positions.dtype, kv_indices.dtype,
+                     kv_indptr.dtype, batch_indices.shape, positions.shape, kv_indptr.shape,
+                     batch_indices.is_contiguous(), positions.is_contiguous(),
+                     kv_indices.is_contiguous(), kv_indptr.is_contiguous(),
+                     batch_indices.device, positions.device, kv_indices.device, kv_indptr.device)
+        _INDEX_ARGS = (batch_indices, positions, kv_indices, kv_indptr)
+        _INDEX_KEY = index_key
+    if type(paged_kv_cache) is torch.Tensor:
+        c0 = paged_kv_cache
+        cache_key = (c0.data_ptr(), c0.shape, c0.stride(), c0.dtype)
     else:
         c0, c1 = paged_kv_cache
-    key = (append_key.data_ptr(), append_value.data_ptr(), batch_indices.data_ptr(),
-           positions.data_ptr(), c0.data_ptr(), c1.data_ptr(), kv_indices.data_ptr(),
-           kv_indptr.data_ptr(), append_key.shape, append_key.stride(), append_value.shape,
-           append_value.stride(), c0.shape, c0.stride(), c1.shape, c1.stride(),
-           append_key.dtype, append_value.dtype, c0.dtype, c1.dtype,
-           batch_indices.dtype, positions.dtype, kv_indices.dtype, kv_indptr.dtype,
-           batch_indices.shape, positions.shape, kv_indices.is_contiguous(), kv_indptr.shape,
-           c0.device, append_key.device, append_value.device, batch_indices.device,
-           positions.device, kv_indices.device, kv_indptr.device, tensor_cache, kv_layout)
+        cache_key = (c0.data_ptr(), c0.shape, c0.stride(), c0.dtype,
+                     c1.data_ptr(), c1.shape, c1.stride(), c1.dtype, c1.device)
+    key = (index_key, cache_key, c0.device, append_key.data_ptr(), append_value.data_ptr(),
+           append_key.shape, append_key.stride(), append_value.shape, append_value.stride(),
+           append_key.dtype, append_value.dtype, kv_layout)
     plan = _PAGED_PLANS.get(key)
     if plan is None:
-        if append_key.shape[0] == 0 and append_key.dim() == 3:
+        if append_key.dim() == 3 and append_key.shape[0] == 0:
             _prepare_paged(append_key, append_value, batch_indices, positions, paged_kv_cache,
                            kv_indices, kv_indptr, kv_layout)
             return

@@ -254,3 +254,32 @@ def test_bf16_rounding_matches_torch():
     ours = W.f32_to_bf16_bits(x)
     ref = torch.from_numpy(x).to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
     assert np.array_equal(ours, ref)
+
+
+def test_host_topology_reads_link_and_local_cpus_from_sysfs(tmp_path, monkeypatch):
+    """PCIe link and local CPU list come from the PCI device's sysfs directory (a fake one
+    here); the affinity is the intersection with what the process may use, and nothing is
+    touched when sysfs has no answer."""
+    import os
+    from lmserve_b200 import host_topology as H
+    assert H.parse_cpu_list("0-3,8,10-11") == [0, 1, 2, 3, 8, 10, 11]
+    monkeypatch.setattr(H, "pci_address", lambda i: "0000:1b:00.0")
+    d = tmp_path / "0000:1b:00.0"
+    d.mkdir()
+    (d / "current_link_speed").write_text("32.0 GT/s PCIe\n")
+    (d / "current_link_width").write_text("16\n")
+    allowed = sorted(os.sched_getaffinity(0))
+    (d / "local_cpulist").write_text(f"{allowed[0]},4000-4001\n")
+    info = H.pcie_link(0, str(tmp_path))
+    assert info["current_link_speed"] == "32.0 GT/s PCIe" and info["current_link_width"] == "16"
+    assert info["max_link_speed"] is None
+    assert H.local_cpus(0, str(tmp_path)) == [allowed[0], 4000, 4001]
+    try:
+        assert H.set_cpu_affinity_for_gpu(0, str(tmp_path)) == [allowed[0]]
+        assert sorted(os.sched_getaffinity(0)) == [allowed[0]]
+    finally:
+        os.sched_setaffinity(0, allowed)
+    (d / "local_cpulist").write_text("\n")
+    assert H.set_cpu_affinity_for_gpu(0, str(tmp_path)) is None
+    monkeypatch.setattr(H, "pci_address", lambda i: None)
+    assert H.pcie_link(0, str(tmp_path)) == {"pci_address": None}
