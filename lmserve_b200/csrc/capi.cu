@@ -664,6 +664,7 @@ int lms_rope_and_cache(const void* query, const void* key, const void* value,
   p.block_size = cached ? block_size : 1;
   p.is_bf16 = dtype;
   p.fused = arithmetic == LMS_ROPE_CONTRACTED ? 1 : 0;
+  p.prefetch = tuned(LMS_TUNE_WRITE_PREFETCH, 1) == 1 ? 1 : 0;
   p.err = ds->err.load(std::memory_order_relaxed);
   p.checks = g_checks.load(std::memory_order_relaxed);
   LMS_CUDA(launch_rope_cache(p, tuned(LMS_TUNE_WRITE_PDL, 1) == 1, (cudaStream_t)stream));

@@ -116,6 +116,7 @@ struct RopeParams {
   int block_size, block_shift;
   int is_bf16;
   int fused;  // 1: contracted as the Triton compiler emits it, 0: every operation rounded
+  int prefetch;  // prefetch the payload lines into L2 before the launch wait
   ErrRecord* err;
   int checks;
 };

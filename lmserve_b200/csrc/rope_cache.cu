@@ -63,35 +63,50 @@ template <class T2, int THREADS, bool FUSED>
 __global__ void __launch_bounds__(THREADS)
 rope_cache_kernel(const RopeParams p, const int items_per_head, const int heads_total,
                   const long long n_items) {
-  // Programmatic dependent launch, as in the cache-write kernel: resident early, but nothing
-  // is touched before the previous kernel of the stream has completed.
-  asm volatile("griddepcontrol.wait;" ::: "memory");
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // item = (t * heads_total + h) * items_per_head + j; the arithmetic needs no memory and is
+  // done before the programmatic-launch wait (32-bit division where the launch allows it)
   const long long item = (long long)blockIdx.x * THREADS + threadIdx.x;
-  if (item >= n_items) return;
-  // item = (t * heads_total + h) * items_per_head + j
-  const int j = (int)(item % items_per_head);
-  const long long q = item / items_per_head;
-  const int h = (int)(q % heads_total);
-  const int t = (int)(q / heads_total);
-
+  int j, h, t;
+  if (n_items <= 0x7fffffffll) {
+    const unsigned it = (unsigned)item;
+    const unsigned q = it / (unsigned)items_per_head;
+    j = (int)(it - q * (unsigned)items_per_head);
+    t = (int)(q / (unsigned)heads_total);
+    h = (int)(q - (unsigned)t * (unsigned)heads_total);
+  } else {
+    j = (int)(item % items_per_head);
+    const long long q = item / items_per_head;
+    h = (int)(q % heads_total);
+    t = (int)(q / heads_total);
+  }
   const int half_bytes = p.head_dim;          // D/2 elements * 2 bytes
   const int head_bytes = 2 * p.head_dim;
   const int vec = j * 16;                     // byte offset of this thread's x vector in the head
+  const bool is_q = h < p.num_heads;
+  const bool is_k = !is_q && h < p.num_heads + p.num_kv_heads;
+  const int kvh = is_q ? 0 : (is_k ? h - p.num_heads : h - p.num_heads - p.num_kv_heads);
+  const char* src = is_q ? p.q + (long long)t * p.q_tok + (long long)h * head_bytes
+                  : is_k ? p.k + (long long)t * p.k_tok + (long long)kvh * head_bytes
+                         : p.v + (long long)t * p.v_tok + (long long)kvh * head_bytes;
+  // Hints only (a prefetch returns nothing and L2 is the point of coherence): the payload
+  // lines start their way into L2 while the previous kernel of the stream is still draining.
+  if (p.prefetch && item < n_items && (vec & 127) == 0) {
+    prefetch_l2(src + vec);
+    prefetch_l2(src + half_bytes + vec);
+  }
+  // Programmatic dependent launch, as in the cache-write kernel: resident early, but nothing
+  // is read or written before the previous kernel of the stream has completed.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (item >= n_items) return;
 
   // Independent loads first: position, slot, payload.
   long long pos = p.pos64 ? reinterpret_cast<const long long*>(p.positions)[t]
                           : (long long)reinterpret_cast<const int*>(p.positions)[t];
-  const bool is_q = h < p.num_heads;
-  const bool is_k = !is_q && h < p.num_heads + p.num_kv_heads;
-  const int kvh = is_q ? 0 : (is_k ? h - p.num_heads : h - p.num_heads - p.num_kv_heads);
   const bool to_cache = !is_q && p.kcache != nullptr;
   long long slot = -1;
   if (to_cache) slot = p.slots[t];
 
-  const char* src = is_q ? p.q + (long long)t * p.q_tok + (long long)h * head_bytes
-                  : is_k ? p.k + (long long)t * p.k_tok + (long long)kvh * head_bytes
-                         : p.v + (long long)t * p.v_tok + (long long)kvh * head_bytes;
   Pack8<T2> x, y;
   ld16(&x, src + vec);
   ld16(&y, src + half_bytes + vec);
