@@ -11,10 +11,11 @@ every layer's paged cache: 256 x 2 KiB x (K, V) read and written per layer = 2 M
 
 Timing protocol of the headline: W untimed warm-up steps; barrier; a few more untimed steps
 inside the region (the first launches after an idle GPU and a collective are not
-representative); then R rounds of exactly K steps, every round bracketed by its own CUDA event
-pair on the launching stream, R chosen so that the region lasts at least 120 ms; `ms_per_step`
-is the MEDIAN round divided by K, max over ranks; best / worst round, the per-rank medians and
-the SM clocks sampled inside that region are reported beside it.  `e2e` times the same step
+representative); then R rounds of exactly K steps, timed in blocks of m consecutive rounds
+(about 2 ms) with one CUDA event pair per block on the launching stream, R chosen so that the
+region lasts at least 120 ms; `ms_per_step` is the MEDIAN block divided by m K, max over
+ranks; best / worst block, the per-rank medians and the SM clocks sampled inside that region
+are reported beside it.  `e2e` times the same step
 through the Python API with key / value / slot_mapping packed in pinned host memory: one
 host-to-device copy per step on a copy stream, double-buffered against the kernel, and the
 library's error record copied back to the host every step.
@@ -200,11 +201,16 @@ def steps_per_graph(steps: int) -> int:
 
 
 def measure_rounds(comm, stream, run_round, steps: int, device_index: int,
-                   min_region_ms: float = 120.0, min_rounds: int = 20, max_rounds: int = 4000):
+                   min_region_ms: float = 120.0, min_blocks: int = 20, max_blocks: int = 2000,
+                   block_ms: float = 2.0):
     """The headline protocol: `run_round()` enqueues exactly `steps` steps.  After a barrier a
-    few rounds run untimed inside the region, then R rounds are timed, each with its own event
-    pair; returns (median round in ms as max over ranks, statistics, per-rank medians in us per
-    step, clocks sampled inside the region)."""
+    few rounds run untimed inside the region, then B blocks of m consecutive rounds are timed,
+    each block with its own event pair; m is chosen so that a block lasts about `block_ms` (an
+    event between two launches costs the programmatic overlap of that one launch, about 9 us:
+    with an event after every 0.2 ms round it would be 4 % of the measurement, per 2 ms block
+    it is 0.4 %), B so that the region lasts at least `min_region_ms`.  Returns (median ms per
+    round as max over ranks, statistics, per-rank medians in us per step, clocks sampled
+    inside the region)."""
     for _ in range(3):
         run_round()
     torch.cuda.synchronize()
@@ -215,10 +221,11 @@ def measure_rounds(comm, stream, run_round, steps: int, device_index: int,
     e1.record(stream)
     torch.cuda.synchronize()
     est = max(e0.elapsed_time(e1) / 3, 1e-3)
-    rounds = int(min(max_rounds, max(min_rounds, math.ceil(min_region_ms / est))))
-    rounds = int(comm.max(float(rounds)))           # the same count on every rank
+    m = max(1, math.ceil(block_ms / est))
+    blocks = int(min(max_blocks, max(min_blocks, math.ceil(min_region_ms / (est * m)))))
+    m, blocks = int(comm.max(float(m))), int(comm.max(float(blocks)))   # the same on every rank
     warm_rounds = max(2, math.ceil(5 / max(1, steps)))
-    events = [torch.cuda.Event(enable_timing=True) for _ in range(rounds + 1)]
+    events = [torch.cuda.Event(enable_timing=True) for _ in range(blocks + 1)]
     torch.cuda.synchronize()
     comm.barrier()
     torch.cuda.synchronize()
@@ -227,18 +234,20 @@ def measure_rounds(comm, stream, run_round, steps: int, device_index: int,
         for _ in range(warm_rounds):
             run_round()
         events[0].record(stream)
-        for r in range(rounds):
-            run_round()
-            events[r + 1].record(stream)
+        for b in range(blocks):
+            for _ in range(m):
+                run_round()
+            events[b + 1].record(stream)
         torch.cuda.synchronize()
     comm.barrier()
-    times = [events[r].elapsed_time(events[r + 1]) for r in range(rounds)]
+    times = [events[b].elapsed_time(events[b + 1]) / m for b in range(blocks)]   # ms per round
     med = statistics.median(times)
-    stats = {"rounds": rounds, "steps_per_round": steps, "in_region_warmup_steps": warm_rounds * steps,
-             "region_ms": round(sum(times), 3),
+    stats = {"rounds": blocks * m, "steps_per_round": steps, "rounds_per_event_pair": m,
+             "event_pairs": blocks, "in_region_warmup_steps": warm_rounds * steps,
+             "region_ms": round(sum(times) * m, 3),
              "us_per_step_median": round(med / steps * 1e3, 4),
-             "us_per_step_best_round": round(min(times) / steps * 1e3, 4),
-             "us_per_step_worst_round": round(max(times) / steps * 1e3, 4),
+             "us_per_step_best": round(min(times) / steps * 1e3, 4),
+             "us_per_step_worst": round(max(times) / steps * 1e3, 4),
              "us_per_step_p10_p90": [round(float(np.percentile(times, q)) / steps * 1e3, 4) for q in (10, 90)]}
     per_rank = [round(x, 4) for x in comm.gather_objects(med / steps * 1e3)]
     return comm.max(med), stats, per_rank, sampler.summary()
@@ -354,7 +363,7 @@ def run_ours(args):
             step_fused(i)
         ms_round, round_stats, per_rank_us, region_clocks = measure_rounds(
             comm, stream, run_round, args.steps, local,
-            **({"min_region_ms": 1.0, "min_rounds": 3} if args.small else {}))
+            **({"min_region_ms": 1.0, "min_blocks": 3, "block_ms": 0.0} if args.small else {}))
         ms_per_step = ms_round / args.steps
         value = world * step_bytes / (ms_per_step * 1e-3) / 1e9
         result.update(ms_per_step=ms_per_step, value=value)
