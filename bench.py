@@ -11,10 +11,10 @@ every layer's paged cache: 256 x 2 KiB x (K, V) read and written per layer = 2 M
 
 Timing protocol of the headline: W untimed warm-up steps; barrier; a few more untimed steps
 inside the region (the first launches after an idle GPU and a collective are not
-representative); then R rounds of exactly K steps, timed in blocks of m consecutive rounds
-(about 2 ms) with one CUDA event pair per block on the launching stream, R chosen so that the
-region lasts at least 120 ms; `ms_per_step` is the MEDIAN block divided by m K, max over
-ranks; best / worst block, the per-rank medians and the SM clocks sampled inside that region
+representative); then R rounds of exactly K steps, issued as replays of one CUDA graph that
+holds m consecutive rounds (about 2 ms of work), every replay with its own CUDA event pair on
+the launching stream, R chosen so that the region lasts at least 120 ms; `ms_per_step` is the
+MEDIAN replay divided by m K, max over ranks; best / worst replay, the per-rank medians and the SM clocks sampled inside that region
 are reported beside it.  `e2e` times the same step
 through the Python API with key / value / slot_mapping packed in pinned host memory: one
 host-to-device copy per step on a copy stream, double-buffered against the kernel, and the
@@ -55,7 +55,6 @@ import workloads as W  # noqa: E402  (input generators only; the product package
 METRIC = "kv_cache_write_bandwidth"
 UNIT = "GB/s"
 ROTATE = 8  # disjoint input sets cycled through so sources never sit in L2
-MAX_GRAPH_STEPS = 64  # most steps captured into one CUDA graph of the headline measurement
 NOMINAL = {"hbm_GB/s": 8000.0, "pcie_gen5_x16_GB/s": 64.0, "nvlink5_GB/s_per_direction": 900.0}
 
 
@@ -188,62 +187,56 @@ def timed(comm, stream, fn, steps: int, warmup: int, sampler=None) -> float:
     return comm.max(e0.elapsed_time(e1))
 
 
-def steps_per_graph(steps: int) -> int:
-    """Steps captured into one CUDA graph so that K steps are a whole number of replays: K
-    itself up to MAX_GRAPH_STEPS, else the largest divisor of K in [8, MAX_GRAPH_STEPS], else
-    40 (the remainder is then launched eagerly)."""
-    if steps <= MAX_GRAPH_STEPS:
-        return max(1, steps)
-    for g in range(MAX_GRAPH_STEPS, 7, -1):
-        if steps % g == 0:
-            return g
-    return 40
+def rounds_per_graph(steps: int, est_step_us: float, target_ms: float = 2.0, max_nodes: int = 512) -> int:
+    """How many rounds of `steps` steps one CUDA graph holds: enough for about `target_ms` of
+    device work, at least one, at most `max_nodes` launches per graph.  Between two graph
+    launches the programmatic overlap of consecutive kernels is lost once (about 8 us on
+    B200); a graph of one 20-step round (0.2 ms) would carry that as 4 % of its time."""
+    per_round_ms = max(steps * est_step_us * 1e-3, 1e-6)
+    m = max(1, math.ceil(target_ms / per_round_ms))
+    return max(1, min(m, max_nodes // max(1, steps)))
 
 
-def measure_rounds(comm, stream, run_round, steps: int, device_index: int,
-                   min_region_ms: float = 120.0, min_blocks: int = 20, max_blocks: int = 2000,
-                   block_ms: float = 2.0):
-    """The headline protocol: `run_round()` enqueues exactly `steps` steps.  After a barrier a
-    few rounds run untimed inside the region, then B blocks of m consecutive rounds are timed,
-    each block with its own event pair; m is chosen so that a block lasts about `block_ms` (an
-    event between two launches costs the programmatic overlap of that one launch, about 9 us:
-    with an event after every 0.2 ms round it would be 4 % of the measurement, per 2 ms block
-    it is 0.4 %), B so that the region lasts at least `min_region_ms`.  Returns (median ms per
-    round as max over ranks, statistics, per-rank medians in us per step, clocks sampled
-    inside the region)."""
+def measure_rounds(comm, stream, run_block, steps: int, rounds_per_block: int, device_index: int,
+                   min_region_ms: float = 120.0, min_blocks: int = 20, max_blocks: int = 2000):
+    """The headline protocol.  `run_block()` enqueues `rounds_per_block` rounds of exactly
+    `steps` steps (one graph replay).  After a barrier a few blocks run untimed inside the
+    region, then B blocks are timed, each with its own CUDA event pair on the launching stream,
+    B chosen so that the region lasts at least `min_region_ms`.  Returns (median ms per round
+    as max over ranks, statistics, per-rank medians in us per step, clocks sampled inside the
+    region)."""
+    m = rounds_per_block
     for _ in range(3):
-        run_round()
+        run_block()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
     for _ in range(3):
-        run_round()
+        run_block()
     e1.record(stream)
     torch.cuda.synchronize()
     est = max(e0.elapsed_time(e1) / 3, 1e-3)
-    m = max(1, math.ceil(block_ms / est))
-    blocks = int(min(max_blocks, max(min_blocks, math.ceil(min_region_ms / (est * m)))))
-    m, blocks = int(comm.max(float(m))), int(comm.max(float(blocks)))   # the same on every rank
-    warm_rounds = max(2, math.ceil(5 / max(1, steps)))
+    blocks = int(min(max_blocks, max(min_blocks, math.ceil(min_region_ms / est))))
+    blocks = int(comm.max(float(blocks)))           # the same count on every rank
+    warm_blocks = max(2, math.ceil(5 / max(1, steps * m)))
     events = [torch.cuda.Event(enable_timing=True) for _ in range(blocks + 1)]
     torch.cuda.synchronize()
     comm.barrier()
     torch.cuda.synchronize()
     sampler = ClockSampler(device_index, period=0.004)
     with sampler:
-        for _ in range(warm_rounds):
-            run_round()
+        for _ in range(warm_blocks):
+            run_block()
         events[0].record(stream)
         for b in range(blocks):
-            for _ in range(m):
-                run_round()
+            run_block()
             events[b + 1].record(stream)
         torch.cuda.synchronize()
     comm.barrier()
     times = [events[b].elapsed_time(events[b + 1]) / m for b in range(blocks)]   # ms per round
     med = statistics.median(times)
     stats = {"rounds": blocks * m, "steps_per_round": steps, "rounds_per_event_pair": m,
-             "event_pairs": blocks, "in_region_warmup_steps": warm_rounds * steps,
+             "event_pairs": blocks, "in_region_warmup_steps": warm_blocks * m * steps,
              "region_ms": round(sum(times) * m, 3),
              "us_per_step_median": round(med / steps * 1e3, 4),
              "us_per_step_best": round(min(times) / steps * 1e3, 4),
@@ -346,30 +339,31 @@ def run_ours(args):
         def step_fused(i):
             fused[i % ROTATE].run(sp)
 
-        # K steps = K // g replays of a CUDA graph of g consecutive steps (one launch each,
-        # cycling through the input sets) plus K % g eager launches; g is chosen so that the
-        # remainder is zero whenever K allows it.
-        g_steps = steps_per_graph(args.steps)
-        n_replay, n_rest = divmod(args.steps, g_steps)
-        fused_graph = graph_of(stream, lambda cs: [fused[j % ROTATE].run(cs) for j in range(g_steps)])
-
-        def run_round():
-            for _ in range(n_replay):
-                fused_graph.replay()
-            for j in range(n_rest):
-                fused[j % ROTATE].run(sp)
-
         for i in range(args.warmup):
             step_fused(i)
+        # A round is exactly K steps.  Rounds are issued as replays of ONE CUDA graph that holds
+        # m consecutive rounds (m x K launches, cycling through the input sets), m chosen for
+        # about 2 ms of device work per replay, and every replay is timed by its own event pair.
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for i in range(50):
+            step_fused(i)
+        e1.record(stream)
+        torch.cuda.synchronize()
+        est_us = e0.elapsed_time(e1) / 50 * 1e3
+        m_rounds = 1 if args.small else int(comm.max(float(rounds_per_graph(args.steps, est_us))))
+        g_steps = m_rounds * args.steps
+        fused_graph = graph_of(stream, lambda cs: [fused[j % ROTATE].run(cs) for j in range(g_steps)])
         ms_round, round_stats, per_rank_us, region_clocks = measure_rounds(
-            comm, stream, run_round, args.steps, local,
-            **({"min_region_ms": 1.0, "min_blocks": 3, "block_ms": 0.0} if args.small else {}))
+            comm, stream, fused_graph.replay, args.steps, m_rounds, local,
+            **({"min_region_ms": 1.0, "min_blocks": 3} if args.small else {}))
         ms_per_step = ms_round / args.steps
         value = world * step_bytes / (ms_per_step * 1e-3) / 1e9
         result.update(ms_per_step=ms_per_step, value=value)
-        how = (f"{n_replay} replay(s) of a CUDA graph of {g_steps} steps"
-               + (f" + {n_rest} eager launches" if n_rest else "")) if n_replay else f"{n_rest} eager launches"
-        graph_launches = (round_stats["rounds"] + 8) * n_replay * g_steps   # replays bypass the C ABI counter
+        how = (f"replays of one CUDA graph of {m_rounds} round(s) x {args.steps} steps = {g_steps} launches, "
+               "one event pair per replay")
+        graph_launches = (round_stats["event_pairs"] + 8) * g_steps   # replays bypass the C ABI counter
 
         # side measurements use at least this many iterations (the profiling case stays short)
         def at_least(n):
@@ -1193,13 +1187,13 @@ def bench_tp8_decode(comm, stream, cache_view, dev, rank, world, peak_gbs, args,
     sp = stream.cuda_stream
     n_e = args.steps if args.small else max(args.steps, 200)
     ms_eager = timed(comm, stream, lambda i: plans[i % ROTATE].run(sp), n_e, 3 if args.small else 10, sampler) / n_e
-    GS = 40
+    GS = 40 if args.small else 240          # about 2 ms of device work per replay
     g = graph_of(stream, lambda cs: [plans[j % ROTATE].run(cs) for j in range(GS)])
     if args.small:
         ms = timed(comm, stream, lambda i: g.replay(), 1, 1, sampler) / GS
         stats, per_rank = None, None
     else:
-        ms_round, stats, per_rank, _ = measure_rounds(comm, stream, g.replay, GS, local, min_region_ms=80.0)
+        ms_round, stats, per_rank, _ = measure_rounds(comm, stream, g.replay, GS, 1, local, min_region_ms=80.0)
         ms = ms_round / GS
     b = wl[0].algorithmic_bytes()
     gbs = b / (ms * 1e-3) / 1e9

@@ -40,11 +40,12 @@ def test_reference_arm_does_not_load_the_product_library():
     assert out.returncode == 0, out.stderr[-2000:]
 
 
-def test_steps_per_graph_divides_the_step_count():
-    assert bench.steps_per_graph(20) == 20 and bench.steps_per_graph(1) == 1
-    assert bench.steps_per_graph(200) == 50 and 200 % bench.steps_per_graph(200) == 0
-    assert bench.steps_per_graph(64) == 64 and bench.steps_per_graph(128) == 64
-    assert bench.steps_per_graph(127) == 40      # a prime above the cap: remainder launched eagerly
+def test_rounds_per_graph_targets_two_milliseconds():
+    assert bench.rounds_per_graph(20, 11.0) == 10           # 10 x 20 x 11 us = 2.2 ms
+    assert bench.rounds_per_graph(200, 11.0) == 1            # one round is already 2.2 ms
+    assert bench.rounds_per_graph(1, 11.0) == 182
+    assert bench.rounds_per_graph(1, 0.5) == 512             # capped by the node count
+    assert bench.rounds_per_graph(1000, 11.0) == 1           # never less than one round
 
 
 def test_profile_traffic_follows_the_kernel():
