@@ -110,7 +110,7 @@ def _pool_from(words):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("engine", ["kernel", "dma"])
+@pytest.mark.parametrize("engine", ["kernel", "dma", "staged"])
 @pytest.mark.parametrize("name", SWAP_CASES)
 def test_gpu_swap_vs_reference_vectors(name, engine):
     from lmserve_b200.ops import cache_ops
@@ -145,6 +145,32 @@ def test_gpu_swap_layer_range_vs_reference_vectors():
         assert np.array_equal(_w(gpu), g["gpu_after_in"])
     finally:
         pool.close()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("engine", ["kernel", "dma", "staged"])
+@pytest.mark.parametrize("name", SWAP_CASES)
+def test_kv_worker_whole_block_copy_kv_vs_reference_vectors(name, engine):
+    """``KVWorker.copy_kv`` without per-layer events (whole blocks in one call) in each of the
+    worker's swap engines; the staged engine is given a staging ring of two blocks so that
+    several groups alternate through its halves."""
+    from lmserve_b200.kv_worker import BlockMapping, Device, KVWorker
+    g = load_npz(name)
+    L, NB, cw = g["gpu_in"].shape
+    gpu = _t(g["gpu_in"]).to(DEV)
+    w = KVWorker("golden", gpu, num_host_blocks=g["host_in"].shape[0], swap_engine=engine,
+                 staging_bytes=2 * L * cw * 2)
+    try:
+        w.host_pool.array.view(np.uint16)[...] = g["host_in"]
+        w.copy_kv([BlockMapping.from_pairs(g["out_pairs"])], Device.GPU, Device.Host)
+        w.dtoh_stream.synchronize()
+        assert np.array_equal(w.host_pool.array.view(np.uint16), g["host_after_out"])
+        w.copy_kv([BlockMapping.from_pairs(g["in_pairs"])], Device.Host, Device.GPU)
+        w.htod_stream.synchronize()
+        assert np.array_equal(_w(gpu), g["gpu_after_in"])
+        assert np.array_equal(w.host_pool.array.view(np.uint16), g["host_after_in"])
+    finally:
+        w.close()
 
 
 @pytest.mark.gpu
