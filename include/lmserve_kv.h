@@ -38,7 +38,7 @@
 extern "C" {
 #endif
 
-#define LMS_VERSION 100 /* major*10000 + minor*100 + patch */
+#define LMS_VERSION 200 /* major*10000 + minor*100 + patch */
 
 typedef enum lms_status {
   LMS_OK = 0,

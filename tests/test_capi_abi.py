@@ -45,7 +45,7 @@ def test_every_declared_symbol_is_exported_and_bound():
 
 def test_version_and_strerror():
     L = _lib.lib()
-    assert L.lms_version() == 100
+    assert L.lms_version() == 200
     assert L.lms_strerror(0) == b"ok"
     for code in range(-7, 0):
         assert L.lms_strerror(code) not in (b"", b"unknown status")
