@@ -226,6 +226,35 @@ def test_transfer_blocks_across_devices():
     assert np.array_equal(to_words(src), src_words)
 
 
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_kv_workers_on_two_gpus_of_one_process_push_and_pull():
+    """Two workers of ONE process on two GPUs: the descriptor names this process, so the peer
+    cache is used in place over NVLink (peer access) instead of through an IPC mapping, which
+    the exporting process could not open.  Push with surplus reservations, then pull back."""
+    shape = W.SHAPES["llama31_70b_tp8"].scaled(num_layers=4, num_blocks=96)
+    src_words, src = make_gpu_cache(shape, 175)
+    dst_words = W.normal_words(np.random.default_rng(176), shape.cache_shape, shape.dtype)
+    dst = to_tensor(dst_words, shape.dtype, "cuda:1")
+    torch.cuda.synchronize("cuda:1")
+    prefill, decode = KVWorker("p0", src), KVWorker("d0", dst)
+    try:
+        local, reserved = [3, 50, 51, 95], [9, 8, 70, 0, 33, 34]
+        assert prefill.push_kv("d0", decode.get_descriptors(reserved), local) is True
+        prefill.push_stream.synchronize()
+        want = dst_words.copy()
+        cache_oracle.transfer(src_words, want, np.stack([local, reserved[:4]], axis=1))
+        assert np.array_equal(to_words(dst), want)
+        # pull other blocks back into the first cache
+        assert prefill.pull_kv("d0", decode.get_descriptors([9, 70]), [60, 61]) is True
+        prefill.push_stream.synchronize()
+        back = src_words.copy()
+        cache_oracle.transfer(want, back, np.array([[9, 60], [70, 61]]))
+        assert np.array_equal(to_words(src), back)
+    finally:
+        prefill.close()
+        decode.close()
+
+
 def test_transfer_blocks_pull_on_one_device_and_argument_errors():
     shape = W.SHAPES["llama31_70b_tp8"].scaled(num_layers=3, num_blocks=40)
     src_words, src = make_gpu_cache(shape, 77)
