@@ -31,16 +31,17 @@ def draw_shape(rng):
     return L, NB, BS, H, D
 
 
-@pytest.mark.parametrize("seed", range(24))
+@pytest.mark.parametrize("seed", range(48))
 def test_fuzz_cache_write(seed):
     rng = np.random.default_rng(9000 + seed)
     L, NB, BS, H, D = draw_shape(rng)
     dtype = "bf16" if seed % 2 else "fp16"
-    variant = int(rng.choice([-1, 0, 1, 2, 3, 4]))
+    variant = int(rng.choice([-1, 0, 1, 2, 3, 4, 5, 6, 7]))
     lib = _lib.lib()
     lib.lms_set_tuning(_lib.TUNE_WRITE_VARIANT, variant)
-    lib.lms_set_tuning(_lib.TUNE_WRITE_TILE_BYTES, int(rng.choice([0, 512, 4096, 65536])))
-    lib.lms_set_tuning(_lib.TUNE_WRITE_VPT, int(rng.choice([0, 2, 4, 8])))
+    lib.lms_set_tuning(_lib.TUNE_WRITE_TILE_BYTES, int(rng.choice([0, 1, 3, 512, 4096, 65536])))
+    lib.lms_set_tuning(_lib.TUNE_WRITE_VPT, int(rng.choice([0, 1, 2, 4, 8])))
+    lib.lms_set_tuning(_lib.TUNE_WRITE_PREFETCH, int(rng.choice([1, 2])))
     T = int(rng.integers(0, min(NB * BS, 300) + 1))
     pad = int(rng.integers(0, 4))                       # extra elements between token rows
     src = W.normal_words(rng, (2, L, T, H * D + pad * 8), dtype)
@@ -103,6 +104,22 @@ def test_fuzz_copy_swap_transfer(seed):
         torch.cuda.synchronize()
         cache_oracle.swap_in(want, host_want, in_pairs, layers=(l0, l1))
         assert np.array_equal(to_words(kv), want), ("swap in", seed, variant)
+        # the same two swaps through the staging ring (a ring of 2 ... 5 blocks, so groups
+        # alternate through its halves), with one or two copy streams
+        if l1 > l0:
+            lib.lms_set_tuning(_lib.TUNE_STAGED_STREAMS, int(rng.choice([1, 2])))
+            per_block = (l1 - l0) * chunk_words * 2
+            ring = torch.empty(int(rng.integers(2, 6)) * per_block + 512, dtype=torch.uint8, device=DEV)
+            out2 = np.stack([rng.permutation(NB)[:m], rng.permutation(NHB)[:m]], axis=1).astype(np.int64)
+            cache_ops.swap_blocks(kv, pool, out2, "out", layers=(l0, l1), engine="staged", staging=ring)
+            torch.cuda.synchronize()
+            cache_oracle.swap_out(want, host_want, out2, layers=(l0, l1))
+            assert np.array_equal(pool.array.view(np.uint16), host_want), ("staged out", seed)
+            in2 = np.stack([np.sort(rng.permutation(NHB)[:m]), rng.permutation(NB)[:m]], axis=1).astype(np.int64)
+            cache_ops.swap_blocks(kv, pool, in2, "in", layers=(l0, l1), engine="staged", staging=ring)
+            torch.cuda.synchronize()
+            cache_oracle.swap_in(want, host_want, in2, layers=(l0, l1))
+            assert np.array_equal(to_words(kv), want), ("staged in", seed)
     finally:
         pool.close()
     # transfer into a second cache, a layer range at a time
@@ -116,3 +133,53 @@ def test_fuzz_copy_swap_transfer(seed):
     if l1 > l0:
         cache_oracle.transfer(want[l0:l1], d_want[l0:l1], tp)
     assert np.array_equal(to_words(dst), d_want), ("transfer", seed, variant)
+
+
+
+@pytest.mark.parametrize("seed", range(16))
+def test_fuzz_paged_append(seed):
+    """flashinfer's (batch index, position, page table) addressing with random request counts,
+    chunk lengths, page sizes and request orders: decode-like steps (one token per request,
+    where the kernel's early fetch of kv_indptr[t] is right), prefill-like steps (where it is
+    wrong) and padded rows; through the cached drop-in and through an explicit plan."""
+    rng = np.random.default_rng(9700 + seed)
+    H, D = int(rng.choice([1, 2, 4])), int(rng.choice([16, 64, 128]))
+    BS = int(rng.choice([1, 4, 16, 32]))
+    nreq = int(rng.integers(1, 40))
+    chunk = 1 if seed % 2 == 0 else int(rng.integers(1, 20))
+    lib = _lib.lib()
+    lib.lms_set_tuning(_lib.TUNE_WRITE_VARIANT, int(rng.choice([-1, 0, 3, 5, 7])))
+    # every request gets its own pages; positions are distinct inside a request
+    pages_per = rng.integers(1, 6, size=nreq)
+    indptr = np.concatenate([[0], np.cumsum(pages_per)]).astype(np.int32)
+    NB = int(indptr[-1]) + 3
+    indices = rng.permutation(NB)[:indptr[-1]].astype(np.int32)
+    batch, pos = [], []
+    for b in range(nreq):
+        room = int(pages_per[b]) * BS
+        take = min(chunk, room)
+        for p in rng.permutation(room)[:take]:
+            batch.append(b)
+            pos.append(int(p))
+    order = rng.permutation(len(batch)) if seed % 3 == 0 else np.arange(len(batch))
+    batch = np.asarray(batch, np.int32)[order]
+    pos = np.asarray(pos, np.int32)[order]
+    T = len(batch)
+    if T > 2:
+        batch[int(rng.integers(0, T))] = -1                 # a padded row
+    key = W.normal_words(rng, (T, H, D), "bf16")
+    value = W.normal_words(rng, (T, H, D), "bf16")
+    cache = W.normal_words(rng, (NB, 2, BS, H, D), "bf16")
+    want = cache.copy()
+    cache_oracle.append_paged_kv_cache(key, value, batch, pos, want, indices, indptr)
+    dev = lambda a: torch.from_numpy(a).to(DEV)
+    k, v = to_tensor(key, "bf16", DEV), to_tensor(value, "bf16", DEV)
+    got = to_tensor(cache, "bf16", DEV)
+    args = (k, v, dev(batch), dev(pos), got, dev(indices), dev(indptr))
+    cache_ops.append_paged_kv_cache(*args, None)
+    torch.cuda.synchronize()
+    assert np.array_equal(to_words(got), want), ("drop-in", seed, nreq, chunk, BS)
+    got.copy_(to_tensor(cache, "bf16", DEV))
+    cache_ops.PagedWritePlan(*args).run()
+    torch.cuda.synchronize()
+    assert np.array_equal(to_words(got), want), ("plan", seed)
