@@ -49,9 +49,7 @@ extern "C" {
                                      cannot change a result); 2 = off */
 #define LMS_TUNE_STAGED_STREAMS 14 /* copy streams lms_swap_blocks_staged spreads its transfers over: 1
                                       (built-in) or 2 */
-#define LMS_TUNE_WRITE_HINT 15    /* experiment: bit 0 = streaming stores, bit 1 = evict-first loads */
-#define LMS_TUNE_WRITE_THREADS 16 /* experiment: CTA size of the one-vector-per-thread write: 128, 256, 512, 1024 */
-#define LMS_TUNE__COUNT 17
+#define LMS_TUNE__COUNT 15
 
 /* Overrides a launch tunable for every later call in this process. */
 int lms_set_tuning(int key, int value);

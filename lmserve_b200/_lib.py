@@ -41,9 +41,7 @@ TUNE_WRITE_PDL = 11
 TUNE_SWAP_ENGINE = 12
 TUNE_WRITE_PREFETCH = 13
 TUNE_STAGED_STREAMS = 14
-TUNE_WRITE_HINT = 15
-TUNE_WRITE_THREADS = 16
-TUNE_COUNT = 17
+TUNE_COUNT = 15
 
 # name -> (restype, argtypes); one entry per declaration in include/lmserve_kv.h and
 # include/lmserve_kv_bench.h

@@ -196,8 +196,6 @@ int write_launch(WriteParams p, void* stream) {
   const int vpt = tuned(LMS_TUNE_WRITE_VPT, 2);
   const bool pdl = tuned(LMS_TUNE_WRITE_PDL, 1) == 1;
   p.prefetch = tuned(LMS_TUNE_WRITE_PREFETCH, 1) == 1 ? 1 : 0;
-  p.hint = tuned(LMS_TUNE_WRITE_HINT, 0);
-  p.threads = tuned(LMS_TUNE_WRITE_THREADS, 0);
   LMS_CUDA(launch_write(p, variant, tile, vpt, ds->sms, pdl, (cudaStream_t)stream));
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return LMS_OK;
