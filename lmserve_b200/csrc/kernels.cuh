@@ -56,8 +56,6 @@ struct WriteParams {
   ErrRecord* err;
   int checks;
   int prefetch;         // untiled kernels: prefetch the source lines into L2 before the launch wait
-  int hint;             // experiment: bit 0 = streaming stores, bit 1 = evict-first loads
-  int threads;          // experiment: CTA size of the one-vector-per-thread kernel (0 = 256)
 };
 
 // variant: 0 = 16-byte vectors, 1 = 32-byte vectors, 2 = bulk copies;

@@ -128,16 +128,6 @@ __device__ __forceinline__ void st_hint(char* p, const V32& r, uint64_t pol) {
       : "memory");
 }
 
-// Streaming ("evict first") stores: the line is marked as the first candidate to leave L2.
-__device__ __forceinline__ void st_cs(char* p, const V16& r) {
-  asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(r.v.x), "r"(r.v.y),
-               "r"(r.v.z), "r"(r.v.w)
-               : "memory");
-}
-__device__ __forceinline__ void st_cs(char* p, const V32& r) {
-  st_hint(p, r, policy_evict_first());
-}
-
 // ---------------------------------------------------------------- bulk copies
 // cp.async.bulk (the untiled TMA path): both addresses 16-byte aligned, size a
 // multiple of 16.  Loads complete on an mbarrier; stores complete through the

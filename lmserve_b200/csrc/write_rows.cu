@@ -233,16 +233,13 @@ write_rows_direct(const WriteParams p, const int row_vecs, const int row_shift,
 
   const SlotRaw raw = slot_fetch_begin(p, layer, t);
   Vec r;
-  if (p.hint & 2) ld_hint(r, src, policy_evict_first());
-  else ld(r, src);
+  ld(r, src);
   const long long off =
       slot_offset(p, slot_fetch_end(p, raw, t), (long long)layer * p.slot_layer + t);
-  if (off >= 0) {
-    char* d = (kv ? p.vcache : p.kcache) + (long long)layer * p.cache_layer + off +
-              (long long)c * Vec::kBytes;
-    if (p.hint & 1) st_cs(d, r);
-    else st(d, r);
-  }
+  if (off >= 0)
+    st((kv ? p.vcache : p.kcache) + (long long)layer * p.cache_layer + off +
+           (long long)c * Vec::kBytes,
+       r);
 }
 
 // A decode step in at most one wave.  Unit u of a layer is (token t, vector c of the row): the
@@ -573,6 +570,32 @@ cudaError_t launch_vec(WriteParams p, int tile_bytes, int sms, cudaStream_t stre
   return cudaGetLastError();
 }
 
+template <class Vec>
+cudaError_t launch_direct(const WriteParams& p, bool pdl, cudaStream_t stream) {
+  constexpr int THREADS = 256;
+  const int row_vecs = p.row_bytes / Vec::kBytes;
+  const int row_shift = ilog2_exact(row_vecs);
+  const long long n_vec = (long long)p.num_layers * p.num_tokens * 2 * row_vecs;
+  const long long ctas = (n_vec + THREADS - 1) / THREADS;
+  if (ctas > 0x7fffffffll) return cudaErrorInvalidConfiguration;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)ctas);
+  cfg.blockDim = dim3(THREADS);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  if (pdl) {
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
+  if (row_shift >= 0)
+    return cudaLaunchKernelEx(&cfg, write_rows_direct<Vec, THREADS, true>, p, row_vecs,
+                              row_shift, n_vec);
+  return cudaLaunchKernelEx(&cfg, write_rows_direct<Vec, THREADS, false>, p, row_vecs,
+                            row_shift, n_vec);
+}
+
 // Launch attributes shared by the untiled kernels.
 struct PdlConfig {
   cudaLaunchConfig_t cfg = {};
@@ -589,28 +612,6 @@ struct PdlConfig {
     }
   }
 };
-
-template <class Vec, int THREADS>
-cudaError_t launch_direct_t(const WriteParams& p, bool pdl, cudaStream_t stream) {
-  const int row_vecs = p.row_bytes / Vec::kBytes;
-  const int row_shift = ilog2_exact(row_vecs);
-  const long long n_vec = (long long)p.num_layers * p.num_tokens * 2 * row_vecs;
-  const long long ctas = (n_vec + THREADS - 1) / THREADS;
-  if (ctas > 0x7fffffffll) return cudaErrorInvalidConfiguration;
-  PdlConfig c(dim3((unsigned)ctas), THREADS, pdl, stream);
-  if (row_shift >= 0)
-    return cudaLaunchKernelEx(&c.cfg, write_rows_direct<Vec, THREADS, true>, p, row_vecs,
-                              row_shift, n_vec);
-  return cudaLaunchKernelEx(&c.cfg, write_rows_direct<Vec, THREADS, false>, p, row_vecs,
-                            row_shift, n_vec);
-}
-template <class Vec>
-cudaError_t launch_direct(const WriteParams& p, bool pdl, cudaStream_t stream) {
-  if (p.threads == 128) return launch_direct_t<Vec, 128>(p, pdl, stream);
-  if (p.threads == 512) return launch_direct_t<Vec, 512>(p, pdl, stream);
-  if (p.threads == 1024) return launch_direct_t<Vec, 1024>(p, pdl, stream);
-  return launch_direct_t<Vec, 256>(p, pdl, stream);
-}
 
 // kind 5: (K, V) vector pairs, TOK units per thread, one CTA tile per THREADS * TOK units;
 // kind 7: the same tiles walked by a persistent grid of `sms * ctas_per_sm` CTAs;
