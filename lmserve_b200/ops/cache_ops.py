@@ -335,8 +335,9 @@ class PagedWritePlan:
 
 _PAGED_PLANS: Dict[tuple, PagedWritePlan] = {}
 _PAGED_PLANS_MAX = 2048
-_INDEX_ARGS: tuple = (None, None, None, None)   # the index tensors of the previous call ...
-_INDEX_KEY: tuple = ()                          # ... and their part of the plan key
+# the index tensors of the previous call and their part of the plan key, as ONE object so that
+# two threads can never pair one call's tensors with another call's key
+_INDEX_CACHE: tuple = ((None, None, None, None), ())
 
 
 def append_paged_kv_cache(
@@ -364,15 +365,20 @@ def append_paged_kv_cache(
 
     This runs once per layer per step with the same buffers, so the validated call is kept as
     a :class:`PagedWritePlan` keyed on everything the validation looked at (addresses, shapes,
-    strides, dtypes); a repeat call is a dictionary lookup and one C call.
+    strides, dtypes); a repeat call is a dictionary lookup and one C call.  The four index
+    tensors are recognised by object identity from one call to the next (they are the same
+    objects for every layer of a step), so re-pointing one of them at other storage in place
+    (``Tensor.set_``) between two calls goes unnoticed; refilling them with ``copy_`` is fine.
     """
     # Two-part key.  The four index tensors are the same Python objects for every layer of a
     # step (``input_params.*`` in LMServe), so their part of the key is recomputed only when
     # one of the objects changes; the per-layer part reads what differs from layer to layer.
-    global _INDEX_ARGS, _INDEX_KEY
-    if (_INDEX_ARGS[0] is batch_indices and _INDEX_ARGS[1] is positions
-            and _INDEX_ARGS[2] is kv_indices and _INDEX_ARGS[3] is kv_indptr):
-        index_key = _INDEX_KEY
+    global _INDEX_CACHE
+    last = _INDEX_CACHE          # one read: (objects, key) is replaced as a whole, never in parts
+    seen = last[0]
+    if (seen[0] is batch_indices and seen[1] is positions
+            and seen[2] is kv_indices and seen[3] is kv_indptr):
+        index_key = last[1]
     else:
         index_key = (batch_indices.data_ptr(), positions.data_ptr(), kv_indices.data_ptr(),
                      kv_indptr.data_ptr(), batch_indices.dtype, positions.dtype, kv_indices.dtype,
@@ -380,8 +386,7 @@ def append_paged_kv_cache(
                      batch_indices.is_contiguous(), positions.is_contiguous(),
                      kv_indices.is_contiguous(), kv_indptr.is_contiguous(),
                      batch_indices.device, positions.device, kv_indices.device, kv_indptr.device)
-        _INDEX_ARGS = (batch_indices, positions, kv_indices, kv_indptr)
-        _INDEX_KEY = index_key
+        _INDEX_CACHE = ((batch_indices, positions, kv_indices, kv_indptr), index_key)
     if type(paged_kv_cache) is torch.Tensor:
         c0 = paged_kv_cache
         cache_key = (c0.data_ptr(), c0.shape, c0.stride(), c0.dtype)
