@@ -171,8 +171,11 @@ def add_kv_worker_servicer(servicer, server: grpc.Server) -> None:
 
 
 def serve(worker: KVWorker, address: str, max_workers: int = 4) -> grpc.Server:
-    """Starts a server for `worker` on `address` (``unix:///path`` as LMServe uses, or
-    ``host:port``) and returns it; stop it with ``server.stop(grace)``."""
+    """Starts a server for `worker` on `address` and returns it; stop it with
+    ``server.stop(grace)``.  Use a Unix socket (``unix:///path``), as LMServe does between its
+    Rust runtime and its workers: the port is unauthenticated and a caller can move KV blocks of
+    any sequence.  ``host:port`` is accepted for tests and for deployments that fence the port
+    themselves; every id and descriptor that arrives is still range-checked by the worker."""
     server = grpc.server(futures.ThreadPoolExecutor(max_workers=max_workers))
     add_kv_worker_servicer(KVWorkerService(worker), server)
     if server.add_insecure_port(address) == 0 and not address.startswith("unix:"):
