@@ -283,3 +283,53 @@ def test_host_topology_reads_link_and_local_cpus_from_sysfs(tmp_path, monkeypatc
     assert H.set_cpu_affinity_for_gpu(0, str(tmp_path)) is None
     monkeypatch.setattr(H, "pci_address", lambda i: None)
     assert H.pcie_link(0, str(tmp_path)) == {"pci_address": None}
+
+
+def _late_recorder(model_queue, kv_queue, layers, delay, log_queue):
+    """Child = the KV process of the CPU handshake test: it 'records' each pre-event (reports it
+    on log_queue) and only then puts the token; afterwards it takes the model's post tokens."""
+    import time
+    time.sleep(delay)
+    for l in range(layers):
+        log_queue.put(("record", f"pre{l}", time.monotonic()))
+        model_queue.put(b"")
+    got = 0
+    for l in range(layers):
+        kv_queue.get(timeout=30)
+        got += 1
+    log_queue.put(("post_tokens", got, time.monotonic()))
+
+
+def test_layer_handshake_across_two_processes_with_queues_only():
+    """The reference's two-process layout without a GPU: the token queues of ``init_cache``
+    (spawn context) carry the 'recorded' signal across the process boundary; the model side's
+    waits are issued only after the KV process has reported its records."""
+    import multiprocessing as mp
+    import time
+    from lmserve_b200.kv_worker import KVWorkerHandle
+    ctx = mp.get_context("spawn")
+    model_queue, kv_queue, log_queue = ctx.Queue(), ctx.Queue(), ctx.Queue()
+    log = []
+    L_ = 3
+    handle = KVWorkerHandle([_FakeEvent(log, f"pre{i}") for i in range(L_)],
+                            [_FakeEvent(log, f"post{i}") for i in range(L_)],
+                            model_queue=model_queue, kv_queue=kv_queue)
+    p = ctx.Process(target=_late_recorder, args=(model_queue, kv_queue, L_, 0.5, log_queue))
+    p.start()
+    waited_at = []
+    stream = _FakeStream(log)
+    for l in range(L_):
+        handle.wait_before_layer(l, stream)      # called at once; returns after the child's token
+        waited_at.append(time.monotonic())
+    for l in range(L_):
+        handle.record_after_layer(l, stream)
+    records = {}
+    for _ in range(L_ + 1):
+        kind, what, when = log_queue.get(timeout=60)
+        records[what if kind == "record" else kind] = (what, when)
+    p.join(timeout=30)
+    assert p.exitcode == 0
+    for l in range(L_):                           # CLOCK_MONOTONIC is shared by both processes
+        assert records[f"pre{l}"][1] <= waited_at[l]
+    assert records["post_tokens"][0] == L_
+    assert [e for e in log if e[0] == "wait"] == [("wait", f"pre{l}") for l in range(L_)]
