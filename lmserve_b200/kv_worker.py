@@ -12,6 +12,7 @@ from __future__ import annotations
 
 import ctypes
 import enum
+import os
 import queue as _queue
 import struct
 from dataclasses import dataclass, field
@@ -215,7 +216,6 @@ class PeerCache:
     enabled when it is on another GPU) when this process exported it."""
 
     def __init__(self, desc: CacheDescriptor):
-        import os
         self.desc = desc
         self.num_layers = desc.num_layers
         self.num_blocks = desc.num_blocks
@@ -389,7 +389,6 @@ def open_disk_pool(path: str, shape) -> np.ndarray:
     """The disk tier's block pool ``[num_disk_blocks, L, chunk_bytes]`` as a writable ``.npy``
     memory map (role of ``memmap_disk_kv_cache``, ``kv_worker.py:48-84``): an existing file of the
     right shape is reused, anything else is replaced by a new file.  Payload is held as bytes."""
-    import os
     shape = tuple(int(x) for x in shape)
     if os.path.exists(path):
         try:
@@ -607,7 +606,6 @@ class KVWorker:
         with torch.cuda.device(self.device):
             _lib.check(_lib.lib().lms_ipc_export(self.gpu_kv_caches.data_ptr(), handle,
                                                  ctypes.byref(offset)))
-        import os
         address = self.gpu_kv_caches.data_ptr()
         _LOCAL_EXPORTS[address] = self.device.index
         return CacheDescriptor(handle.raw, offset.value, self.device.index, self.num_layers,
