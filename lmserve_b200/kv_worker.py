@@ -420,7 +420,7 @@ class KVWorker:
             raise ValueError("swap_engine must be 'kernel', 'dma' or 'staged'")
         # "kernel": the sm_100a gather/scatter kernel on 3 CTAs - 0.92 of the PCIe memcpy rate
         # even when launched once per layer, at a cost of about 10 % to concurrent full-SM GEMMs.
-        # "dma": copy engines only, no SM is touched; full rate needs many layers per launch
+        # "dma": copy engines only, no SM is touched; its rate (0.89 of memcpy) needs many layers per launch
         # (one 64 KiB copy per layer and block, the reference's pattern, reaches 13 GB/s).
         # "staged": whole-block swaps through a device staging ring and one DMA transfer per
         # host block; swaps that are pipelined layer by layer fall back to the kernel.

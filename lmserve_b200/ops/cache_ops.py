@@ -641,7 +641,9 @@ def swap_blocks(
     upwards, the copy-engine form nothing.  ``engine="staged"`` gathers groups of blocks into
     ``staging`` (a device tensor of the caller, at least two blocks' worth of bytes; 128 MiB
     and more is sensible) and lets the copy engines move whole host blocks in one transfer each
-    (``lms_swap_blocks_staged``): the form for swapping many whole blocks at the full PCIe rate.
+    (``lms_swap_blocks_staged``): the form for swapping many whole blocks; it reaches the rate of
+    a plain pinned ``cudaMemcpy`` when the host blocks of the call are adjacent, and the kernel's
+    rate when they are scattered.
     """
     _require_cuda("gpu_kv_caches", gpu_kv_caches)
     if direction not in ("out", "in"):
