@@ -37,7 +37,7 @@ extern "C" {
 #define LMS_TUNE_XFER_VARIANT 8  /* as LMS_TUNE_COPY_VARIANT */
 #define LMS_TUNE_WRITE_VPT 9     /* vectors per thread per pipeline batch of the cache write: 2, 4, 8 */
 #define LMS_TUNE_SWAP_VARIANT 10 /* as LMS_TUNE_COPY_VARIANT, both directions */
-#define LMS_TUNE_WRITE_PDL 11    /* 1 (built-in) = launch the untiled cache write and the rotary kernel
+#define LMS_TUNE_WRITE_PDL 11    /* 1 (built-in) = launch the untiled cache write, the untiled chunk copy and the rotary kernel
                                     with programmatic stream serialization: the grid becomes resident
                                     while the previous kernel drains and still waits for that kernel
                                     before touching memory, so stream order is unchanged; 2 = off */

@@ -255,6 +255,7 @@ int chunk_copy(const void* src, int64_t src_layer, int64_t src_block, void* dst,
   p.err = ds->err.load(std::memory_order_relaxed);
   p.where = where;
   p.checks = g_checks.load(std::memory_order_relaxed);
+  p.pdl = tuned(LMS_TUNE_WRITE_PDL, 1) == 1 ? 1 : 0;
 
   if (ctas <= 0) ctas = ds->sms * 8;
   LMS_CUDA(launch_chunk_copy(p, variant, policy, ctas, (cudaStream_t)stream));

@@ -120,7 +120,6 @@ __global__ void __launch_bounds__(THREADS)
 chunk_copy_direct(const CopyParams p, const int chunk_vecs, const int chunk_shift,
                   const long long n_vec_total) {
   const long long v = (long long)blockIdx.x * THREADS + threadIdx.x;
-  if (v >= n_vec_total) return;
   long long q;
   int c;
   if (chunk_shift >= 0) {
@@ -138,6 +137,12 @@ chunk_copy_direct(const CopyParams p, const int chunk_vecs, const int chunk_shif
     pair = q / p.num_layers;
     layer = q - pair * p.num_layers;
   }
+  // Programmatic dependent launch (a no-op when the launch does not ask for it): the grid may
+  // be resident while the previous kernel of the stream drains; nothing is read or written
+  // before that kernel has completed, so stream order is unchanged.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (v >= n_vec_total) return;
   const longlong2 sd = reinterpret_cast<const longlong2*>(p.pairs)[pair];
   if (p.checks) {
     if (sd.x < 0 || (p.num_src_blocks > 0 && sd.x >= p.num_src_blocks)) {
@@ -261,8 +266,18 @@ cudaError_t launch_direct(const CopyParams& p, cudaStream_t stream) {
   const long long n_vec = (long long)p.num_layers * p.n_pairs * chunk_vecs;
   const long long ctas = (n_vec + THREADS - 1) / THREADS;
   if (ctas > 0x7fffffffll) return cudaErrorInvalidConfiguration;
-  chunk_copy_direct<Vec, THREADS, POLICY><<<(unsigned)ctas, THREADS, 0, stream>>>(p, chunk_vecs, shift, n_vec);
-  return cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)ctas);
+  cfg.blockDim = dim3(THREADS);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  if (p.pdl) {
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
+  return cudaLaunchKernelEx(&cfg, chunk_copy_direct<Vec, THREADS, POLICY>, p, chunk_vecs, shift, n_vec);
 }
 
 }  // namespace

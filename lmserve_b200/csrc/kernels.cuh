@@ -86,6 +86,7 @@ struct CopyParams {
   ErrRecord* err;
   unsigned int where;
   int checks;
+  int pdl;           // untiled kernel: launch with programmatic stream serialization
 };
 
 // variant as above; policy: 0 = default caching, 1 = sources kept in L2 and

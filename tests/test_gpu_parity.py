@@ -519,6 +519,38 @@ def test_append_paged_decode_step_plan_is_reused_and_guess_may_be_wrong(variant)
     assert np.array_equal(to_words(got), want2)
 
 
+def test_write_then_copy_on_write_chains_land_in_stream_order():
+    """Cache write and copy-on-write launched back to back on one stream, each with
+    programmatic stream serialization: every copy must see the rows written just before it and
+    every write the blocks copied just before it, over many rounds without a synchronize."""
+    shape = W.SHAPES["llama31_8b"].scaled(num_layers=2, num_blocks=64, num_kv_heads=2)
+    rng = np.random.default_rng(321)
+    cache = W.normal_words(rng, shape.cache_shape, shape.dtype)
+    got = to_tensor(cache, shape.dtype, DEV)
+    want = cache.copy()
+    rounds = 12
+    keys = W.normal_words(rng, (rounds, 2, 16, 2, 128), shape.dtype)
+    vals = W.normal_words(rng, (rounds, 2, 16, 2, 128), shape.dtype)
+    d_keys, d_vals = to_tensor(keys, shape.dtype, DEV), to_tensor(vals, shape.dtype, DEV)
+    plan = []
+    for r in range(rounds):
+        blk = int(rng.integers(0, 32))                       # written block
+        dst = int(rng.integers(32, 64))                      # its copy
+        slots = (blk * 16 + rng.permutation(16)).astype(np.int64)
+        plan.append((slots, np.array([[blk, dst]], dtype=np.int64)))
+    d_slots = [torch.from_numpy(s).to(DEV) for s, _ in plan]
+    d_pairs = [torch.from_numpy(p).to(DEV) for _, p in plan]
+    torch.cuda.synchronize()
+    for r in range(rounds):
+        cache_ops.reshape_and_cache_layers(d_keys[r], d_vals[r], got, d_slots[r])
+        cache_ops.copy_blocks(got, d_pairs[r])
+    torch.cuda.synchronize()
+    for r, (slots, pairs) in enumerate(plan):
+        cache_oracle.reshape_and_cache_layers(keys[r], vals[r], want, slots)
+        cache_oracle.copy_blocks(want, pairs)
+    assert np.array_equal(to_words(got), want)
+
+
 def test_append_paged_kv_cache_matches_flashinfer():
     """The reference's live cache write is flashinfer's kernel; where flashinfer is importable on
     the GPU box, its result on the same inputs is the golden output."""
