@@ -28,7 +28,7 @@ import asyncio
 import ctypes
 import enum
 import importlib.util
-import pickle
+import json
 import queue
 import sys
 import types
@@ -132,10 +132,10 @@ class FakeNixlAgent:
         return _DescList((t.data_ptr(), t.numel() * t.element_size()) for t in tensors)
 
     def get_serialized_descs(self, descs) -> bytes:
-        return pickle.dumps(descs.descs)
+        return json.dumps(descs.descs).encode()
 
     def deserialize_descs(self, blob: bytes):
-        return _DescList(pickle.loads(blob))
+        return _DescList(tuple(d) for d in json.loads(bytes(blob).decode()))
 
     def initialize_xfer(self, op, local, remote, peer_name, notif=b""):
         if op not in ("WRITE", "READ") or local.descCount() != remote.descCount():
