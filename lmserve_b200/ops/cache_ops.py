@@ -226,6 +226,17 @@ def reshape_and_cache_layers(
     _write_layers(key, value, kv_caches, slot_mapping)
 
 
+_plan_run_address = None
+
+
+def _PLAN_RUN_ADDRESS() -> int:
+    """Address of ``lms_write_plan_run`` in the loaded library (looked up once)."""
+    global _plan_run_address
+    if _plan_run_address is None:
+        _plan_run_address = ctypes.cast(_lib.lib().lms_write_plan_run, ctypes.c_void_p).value
+    return _plan_run_address
+
+
 def _prepare_paged(append_key, append_value, batch_indices, positions, paged_kv_cache,
                    kv_indices, kv_indptr, kv_layout):
     """Validates a paged append and returns (device, argument tuple of
@@ -301,7 +312,7 @@ class PagedWritePlan:
     records addresses and geometry, not tensors: it must be rebuilt when a tensor is
     reallocated (``append_paged_kv_cache`` does that by itself)."""
 
-    __slots__ = ("device", "_handle", "_run", "_destroy", "_index")
+    __slots__ = ("device", "_handle", "_fn", "_plan", "_destroy", "_index")
 
     def __init__(self, append_key, append_value, batch_indices, positions, paged_kv_cache,
                  kv_indices, kv_indptr, kv_last_page_len=None, kv_layout: str = "NHD"):
@@ -313,8 +324,9 @@ class PagedWritePlan:
         with torch.cuda.device(self.device):
             _lib.check(L_.lms_paged_write_plan_create(*args, ctypes.byref(handle)))
         self._handle = handle
-        self._run = L_.lms_write_plan_run
         self._destroy = L_.lms_write_plan_destroy
+        self._fn = _PLAN_RUN_ADDRESS()
+        self._plan = handle.value or 0
 
     def run(self, stream: Optional[int] = None) -> None:
         """Enqueues the append on `stream` (a raw ``cudaStream_t`` value; default: the current
@@ -322,7 +334,7 @@ class PagedWritePlan:
         if stream is None:
             stream = _raw_stream(self._index) if _raw_stream is not None else \
                 torch.cuda.current_stream(self.device).cuda_stream
-        rc = self._run(self._handle, stream)
+        rc = _packer.call_plan(self._fn, self._plan, stream)
         if rc:
             _lib.check(rc)
 
@@ -512,8 +524,11 @@ class WritePlan:
             # call inside a graph capture
             _lib.check(_lib.lib().lms_write_plan_create(*args, ctypes.byref(handle)))
         self._handle = handle
-        self._run = _lib.lib().lms_write_plan_run
         self._destroy = _lib.lib().lms_write_plan_destroy
+        # run() goes through the C helper: address of lms_write_plan_run + the plan's address,
+        # no ctypes argument conversion on the per-layer path
+        self._fn = _PLAN_RUN_ADDRESS()
+        self._plan = handle.value or 0
 
     def run(self, stream: Optional[int] = None) -> None:
         """Enqueues the write on `stream` (a raw ``cudaStream_t`` value such as
@@ -521,7 +536,7 @@ class WritePlan:
         current CUDA device must be the plan's device."""
         if stream is None:
             stream = torch.cuda.current_stream(self.device).cuda_stream
-        rc = self._run(self._handle, stream)
+        rc = _packer.call_plan(self._fn, self._plan, stream)
         if rc:
             _lib.check(rc)
 

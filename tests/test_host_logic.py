@@ -333,3 +333,15 @@ def test_layer_handshake_across_two_processes_with_queues_only():
         assert records[f"pre{l}"][1] <= waited_at[l]
     assert records["post_tokens"][0] == L_
     assert [e for e in log if e[0] == "wait"] == [("wait", f"pre{l}") for l in range(L_)]
+
+
+def test_plan_call_helper_goes_through_the_c_abi():
+    """``_packer.call_plan`` calls ``lms_write_plan_run`` by address: a NULL plan is refused by
+    the library itself (LMS_ERR_NULL), before any CUDA call, and a NULL address by the helper."""
+    from lmserve_b200 import _lib, _packer
+    fn = cache_ops._PLAN_RUN_ADDRESS()
+    assert fn and _packer.call_plan(fn, 0, 0) == _lib.LMS_ERR_NULL
+    with pytest.raises(ValueError):
+        _packer.call_plan(0, 0, 0)
+    with pytest.raises(TypeError):
+        _packer.call_plan(fn, 0)
