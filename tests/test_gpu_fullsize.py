@@ -112,7 +112,8 @@ def test_prefill_and_cow_qwen25_7b_full(pool):
     assert bool((flat[0].index_select(0, src[:16]) != 0).any())            # and not trivially zero
 
 
-def test_swap_round_trip_llama31_8b_full(pool):
+@pytest.mark.parametrize("engine", ["kernel", "staged"])
+def test_swap_round_trip_llama31_8b_full(pool, engine):
     s = W.SHAPES["llama31_8b_swap"]
     kv = view(pool, s)
     per_block = s.num_layers * s.chunk_bytes
@@ -132,8 +133,9 @@ def test_swap_round_trip_llama31_8b_full(pool):
         ramp = torch.arange(n_blocks, device=DEV, dtype=torch.float32)[:, None]
         for l in range(s.num_layers):
             flat[l].index_copy_(0, src, (base + ramp * (0.001 * (l + 1))).to(torch.bfloat16))
-        cache_ops.swap_blocks(kv, host, w.out_pairs, "out")
-        cache_ops.swap_blocks(kv, host, w.in_pairs, "in")
+        staging = torch.empty(256 << 20, dtype=torch.uint8, device=DEV) if engine == "staged" else None
+        cache_ops.swap_blocks(kv, host, w.out_pairs, "out", engine=engine, staging=staging)
+        cache_ops.swap_blocks(kv, host, w.in_pairs, "in", engine=engine, staging=staging)
         torch.cuda.synchronize()
         back = {int(h): int(g) for g, h in w.out_pairs}
         src_of_dst = torch.tensor([back[int(h)] for h in w.in_pairs[:, 0]], device=DEV)
