@@ -6,17 +6,23 @@
 // HBM bandwidth: 2 * row_bytes read and 2 * row_bytes written per live token
 // per layer.
 //
-// Three implementations share one parameter block (write_rows_direct is the default):
-//   * write_rows_vec  - a CTA owns a tile of tokens of one layer.  Slot loads and
-//     the first batch of payload loads are issued together; the slots are then
-//     turned into destination byte offsets once, in shared memory, and the tile
-//     is streamed as a two-stage software pipeline of 16- or 32-byte vectors
-//     (loads of batch b+1 in flight while batch b is stored).
-//   * write_rows_direct - no tile and no shared memory: thread i owns vector i of
-//     the whole launch, issues its index loads and payload load together, stores.
-//   * write_rows_bulk - every lane of a warp owns one piece of a row and moves
-//     it with a bulk (TMA) copy global -> shared -> global; the warp shares one
-//     mbarrier.  Almost no instructions per byte.
+// Several implementations share one parameter block.  write_rows_direct is the one the library
+// launches by itself; the others were built to be measured against it (they are parity-tested
+// and can be selected through the launch tunables) and lost:
+//   * write_rows_direct - no tile and no shared memory: thread i owns vector i of the whole
+//     launch.  Index arithmetic and an L2 prefetch of its source line come before the
+//     programmatic-launch wait, then it issues its index loads and payload load together and
+//     stores.
+//   * write_rows_pair / write_rows_multi - the same idea with 2 ... 8 vectors per thread in a
+//     grid of at most one wave (a thread moves the K and the V vector of 1, 2 or 4 tokens, or
+//     2 / 4 independent vectors); write_rows_pair_persistent walks the same tiles with a
+//     persistent grid and a two-deep register pipeline.
+//   * write_rows_vec  - a CTA owns a tile of tokens of one layer.  Slot loads and the first
+//     batch of payload loads are issued together; the slots are then turned into destination
+//     byte offsets once, in shared memory, and the tile is streamed as a two-stage software
+//     pipeline of 16- or 32-byte vectors (loads of batch b+1 in flight while batch b is stored).
+//   * write_rows_bulk - every lane of a warp owns one piece of a row and moves it with a bulk
+//     (TMA) copy global -> shared -> global; the warp shares one mbarrier with a bounded wait.
 #include "kernels.cuh"
 
 namespace lms {
