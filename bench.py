@@ -734,6 +734,40 @@ def bench_rope_fusion(comm, stream, cache_view, dev, args, sampler):
     return out
 
 
+def reference_way(inputs, dev, flashinfer=None, page_size=16):
+    """LMServe's own way to prepare a step's index tensors (model_worker.py:310-433), restated
+    as the timed baseline: Python lists, one torch.tensor(...).to('cuda') per array and
+    flashinfer's two helpers (a torch restatement of them when flashinfer is absent)."""
+    flatten_input_ids, position_ids, seqlens_q = [], [], []
+    inputs.sort(key=lambda x: -x.input_len)
+    for data in inputs:
+        flatten_input_ids += data.input_ids
+        position_ids += [i for i in range(data.filled_token_len, data.context_len)]
+        seqlens_q.append(data.input_len)
+    ids = torch.tensor(flatten_input_ids, dtype=torch.long).to(dev, non_blocking=True)
+    pos_ids = torch.tensor(position_ids, dtype=torch.int).to(dev, non_blocking=True)
+    cu_q = torch.tensor(np.cumsum([0] + seqlens_q), dtype=torch.int).to(dev, non_blocking=True)
+    kv_block_indices, num_blocks_per_seqs, kv_last_block_lens = [], [], []
+    for data in inputs:
+        kv_block_indices += data.block_ids
+        num_blocks_per_seqs.append(len(data.block_ids))
+        kv_last_block_lens.append((data.context_len - 1) % page_size + 1)
+    indptr = torch.tensor(np.cumsum([0] + num_blocks_per_seqs), dtype=torch.int).to(dev, non_blocking=True)
+    indices = torch.tensor(kv_block_indices, dtype=torch.int).to(dev, non_blocking=True)
+    last = torch.tensor(kv_last_block_lens, dtype=torch.int).to(dev, non_blocking=True)
+    nnz = sum(seqlens_q)
+    if flashinfer is not None:
+        b, p = flashinfer.get_batch_indices_positions(
+            cu_q, flashinfer.get_seq_lens(indptr, last, page_size), nnz)
+    else:
+        seq = torch.clamp(indptr[1:] - indptr[:-1] - 1, min=0) * page_size + last
+        q = cu_q[1:] - cu_q[:-1]
+        b = torch.repeat_interleave(torch.arange(len(inputs), device=dev, dtype=torch.int), q.long())
+        p = (torch.arange(nnz, device=dev, dtype=torch.int) - cu_q[b.long()] + (seq - q)[b.long()]).int()
+    return ids, pos_ids, cu_q, indptr, indices, last, b, p
+
+
+
 def bench_index_prep(comm, stream, dev, args, sampler):
     """Per-step index preparation, host wall time per step with a synchronize at the end (the
     forward pass cannot start before its indices exist): LMServe's way — Python lists, one
@@ -749,34 +783,8 @@ def bench_index_prep(comm, stream, dev, args, sampler):
     except Exception:  # noqa: BLE001
         flashinfer = None
 
-    def reference_way(inputs, page_size=16):
-        flatten_input_ids, position_ids, seqlens_q = [], [], []
-        inputs.sort(key=lambda x: -x.input_len)
-        for data in inputs:
-            flatten_input_ids += data.input_ids
-            position_ids += [i for i in range(data.filled_token_len, data.context_len)]
-            seqlens_q.append(data.input_len)
-        ids = torch.tensor(flatten_input_ids, dtype=torch.long).to(dev, non_blocking=True)
-        pos_ids = torch.tensor(position_ids, dtype=torch.int).to(dev, non_blocking=True)
-        cu_q = torch.tensor(np.cumsum([0] + seqlens_q), dtype=torch.int).to(dev, non_blocking=True)
-        kv_block_indices, num_blocks_per_seqs, kv_last_block_lens = [], [], []
-        for data in inputs:
-            kv_block_indices += data.block_ids
-            num_blocks_per_seqs.append(len(data.block_ids))
-            kv_last_block_lens.append((data.context_len - 1) % page_size + 1)
-        indptr = torch.tensor(np.cumsum([0] + num_blocks_per_seqs), dtype=torch.int).to(dev, non_blocking=True)
-        indices = torch.tensor(kv_block_indices, dtype=torch.int).to(dev, non_blocking=True)
-        last = torch.tensor(kv_last_block_lens, dtype=torch.int).to(dev, non_blocking=True)
-        nnz = sum(seqlens_q)
-        if flashinfer is not None:
-            b, p = flashinfer.get_batch_indices_positions(
-                cu_q, flashinfer.get_seq_lens(indptr, last, page_size), nnz)
-        else:
-            seq = torch.clamp(indptr[1:] - indptr[:-1] - 1, min=0) * page_size + last
-            q = cu_q[1:] - cu_q[:-1]
-            b = torch.repeat_interleave(torch.arange(len(inputs), device=dev, dtype=torch.int), q.long())
-            p = (torch.arange(nnz, device=dev, dtype=torch.int) - cu_q[b.long()] + (seq - q)[b.long()]).int()
-        return ids, pos_ids, cu_q, indptr, indices, last, b, p
+    def reference_way_here(inputs):
+        return reference_way(inputs, dev, flashinfer)
 
     cases = {
         "decode_256_requests": dict(num_decode=256, ctx_lo=128, ctx_hi=4096, num_prefill=0,
@@ -788,7 +796,7 @@ def bench_index_prep(comm, stream, dev, args, sampler):
     out = {"flashinfer_helpers": flashinfer is not None}
     for name, kw in cases.items():
         reqs = [W.make_step_requests(65536, 16, seed=6000 + i, **kw) for i in range(4)]
-        ref = reference_way(copy.copy(reqs[0]))
+        ref = reference_way_here(copy.copy(reqs[0]))
         ids, s = builder.make_inputs(copy.copy(reqs[0]))
         torch.cuda.synchronize()
         same = (torch.equal(ref[0], ids) and torch.equal(ref[1], s.position_ids)
@@ -797,7 +805,7 @@ def bench_index_prep(comm, stream, dev, args, sampler):
                 and torch.equal(ref[6], s.batch_indices) and torch.equal(ref[7], s.positions))
         res = {"results_match": bool(same), "tokens": int(ids.numel()),
                "block_table_entries": int(s.kv_block_indices.numel())}
-        for label, fn in (("reference_way_us", reference_way), ("one_upload_one_kernel_us", builder.make_inputs)):
+        for label, fn in (("reference_way_us", reference_way_here), ("one_upload_one_kernel_us", builder.make_inputs)):
             times = []
             for i in range(23):
                 r = copy.copy(reqs[i % 4])
@@ -1147,6 +1155,42 @@ def bench_vs_flashinfer(comm, stream, cache_view, dev, args, sampler):
         ms_g = statistics.median(timed(comm, stream, lambda i: graphs[i % ROTATE].replay(), 100, 5, sampler)
                                  for _ in range(5)) / 100
         out[name] = {"eager_us_per_layer": ms_e * 1e3 / Lyr, "graph_us_per_layer": ms_g * 1e3 / Lyr}
+    # The cache path of a whole decode step as a model worker runs it, host wall time from the
+    # request objects to all 32 layers' rows in the cache (synchronised at the end): LMServe's
+    # way (its index preparation + 32 flashinfer appends) against ModelStepCache (one packed
+    # upload + one index kernel + 32 cached-plan appends).  K / V are ready on the device.
+    import copy
+    from lmserve_b200.model_step import ModelStepCache
+    step_cache = ModelStepCache(kv, max_batch=256, max_tokens=4096, max_blocks=131072)
+    reqs = [W.make_step_requests(s.num_blocks, 16, seed=8100 + i, num_decode=256, ctx_lo=128, ctx_hi=4096,
+                                 num_prefill=0, chunk_tokens=0, max_offset=0) for i in range(4)]
+    k0, v0 = sets[0]["key"], sets[0]["value"]
+
+    def step_reference(r):
+        ref = reference_way(r, dev, flashinfer)
+        for l in range(Lyr):
+            flashinfer.append_paged_kv_cache(k0[l], v0[l], ref[6], ref[7], kv[l], ref[4], ref[3], ref[5])
+
+    def step_ours(r):
+        _, params = step_cache.begin_step(r)
+        for l in range(Lyr):
+            step_cache.write_layer(l, k0[l], v0[l], params)
+
+    whole = {}
+    for label, fn in (("lmserve_way_us", step_reference), ("this_library_us", step_ours)):
+        times = []
+        for i in range(13):
+            r = copy.copy(reqs[i % 4])
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            fn(r)
+            torch.cuda.synchronize()
+            times.append(time.perf_counter() - t0)
+        whole[label] = float(np.median(times[3:])) * 1e6
+    whole["speedup"] = whole["lmserve_way_us"] / whole["this_library_us"]
+    whole["note"] = ("host wall time of one decode step's cache path, 256 requests x 32 layers: index "
+                     "preparation from the request objects + the 32 per-layer cache writes, eager")
+    out["decode_step_cache_path"] = whole
     f = out["flashinfer"]
     d = out["ours_flashinfer_signature"]
     out["drop_in_vs_flashinfer"] = {"eager_speedup": f["eager_us_per_layer"] / d["eager_us_per_layer"],
