@@ -16,32 +16,44 @@
 #include <Python.h>
 #include <stdint.h>
 
-static int get_i32(PyObject* obj, const char* name, int32_t* out) {
-  PyObject* v = PyObject_GetAttrString(obj, name);
-  if (!v) return -1;
-  long long x = PyLong_AsLongLong(v);
-  Py_DECREF(v);
-  if (x == -1 && PyErr_Occurred()) return -1;
+/* Attribute names, interned once at module start-up (a lookup by C string builds a new str
+ * object per call). */
+static PyObject *s_input_len, *s_filled_token_len, *s_context_len, *s_block_ids, *s_input_ids;
+
+/* Value of a Python int: the one-digit ("compact") form that every id, length and position here
+ * has is read in place; anything else takes the general conversion. */
+static inline int as_i32(PyObject* v, int32_t* out, const char* what) {
+  long long x;
+#if PY_VERSION_HEX >= 0x030C0000
+  if (PyLong_CheckExact(v) && PyUnstable_Long_IsCompact((const PyLongObject*)v)) {
+    x = (long long)PyUnstable_Long_CompactValue((const PyLongObject*)v);
+  } else
+#endif
+  {
+    x = PyLong_AsLongLong(v);
+    if (x == -1 && PyErr_Occurred()) return -1;
+  }
   if (x < INT32_MIN || x > INT32_MAX) {
-    PyErr_Format(PyExc_OverflowError, "%s does not fit 32 bits", name);
+    PyErr_Format(PyExc_OverflowError, "%s does not fit 32 bits", what);
     return -1;
   }
   *out = (int32_t)x;
   return 0;
 }
 
+static int get_i32(PyObject* obj, PyObject* name, const char* what, int32_t* out) {
+  PyObject* v = PyObject_GetAttr(obj, name);
+  if (!v) return -1;
+  const int rc = as_i32(v, out, what);
+  Py_DECREF(v);
+  return rc;
+}
+
 /* Copies the integers of `seq` (already a list or tuple) to dst[0..n). */
 static int copy_ints(PyObject* fast, Py_ssize_t n, int32_t* dst, const char* what) {
   PyObject** items = PySequence_Fast_ITEMS(fast);
-  for (Py_ssize_t i = 0; i < n; ++i) {
-    long long x = PyLong_AsLongLong(items[i]);
-    if (x == -1 && PyErr_Occurred()) return -1;
-    if (x < INT32_MIN || x > INT32_MAX) {
-      PyErr_Format(PyExc_OverflowError, "%s entry does not fit 32 bits", what);
-      return -1;
-    }
-    dst[i] = (int32_t)x;
-  }
+  for (Py_ssize_t i = 0; i < n; ++i)
+    if (as_i32(items[i], dst + i, what)) return -1;
   return 0;
 }
 
@@ -83,15 +95,16 @@ static PyObject* pack(PyObject* self, PyObject* args) {
     for (Py_ssize_t b = 0; b < batch; ++b) {
       PyObject* r = PySequence_Fast_GET_ITEM(reqs, b);
       int32_t q, filled, ctx;
-      if (get_i32(r, "input_len", &q) || get_i32(r, "filled_token_len", &filled) ||
-          get_i32(r, "context_len", &ctx))
+      if (get_i32(r, s_input_len, "input_len", &q) ||
+          get_i32(r, s_filled_token_len, "filled_token_len", &filled) ||
+          get_i32(r, s_context_len, "context_len", &ctx))
         goto done;
-      PyObject* a = PyObject_GetAttrString(r, "block_ids");
+      PyObject* a = PyObject_GetAttr(r, s_block_ids);
       if (!a) goto done;
       blocks[b] = PySequence_Fast(a, "block_ids must be a sequence");
       Py_DECREF(a);
       if (!blocks[b]) goto done;
-      a = PyObject_GetAttrString(r, "input_ids");
+      a = PyObject_GetAttr(r, s_input_ids);
       if (!a) goto done;
       ids[b] = PySequence_Fast(a, "input_ids must be a sequence");
       Py_DECREF(a);
@@ -280,4 +293,12 @@ static struct PyModuleDef module = {PyModuleDef_HEAD_INIT, "_packer",
                                     "Packs a step's request list into the index-preparation upload buffer.",
                                     -1, methods};
 
-PyMODINIT_FUNC PyInit__packer(void) { return PyModule_Create(&module); }
+PyMODINIT_FUNC PyInit__packer(void) {
+  s_input_len = PyUnicode_InternFromString("input_len");
+  s_filled_token_len = PyUnicode_InternFromString("filled_token_len");
+  s_context_len = PyUnicode_InternFromString("context_len");
+  s_block_ids = PyUnicode_InternFromString("block_ids");
+  s_input_ids = PyUnicode_InternFromString("input_ids");
+  if (!s_input_len || !s_filled_token_len || !s_context_len || !s_block_ids || !s_input_ids) return NULL;
+  return PyModule_Create(&module);
+}

@@ -126,6 +126,18 @@ def test_c_packer_and_python_packer_agree(monkeypatch):
     bad[0].block_ids = [1 << 40]
     with pytest.raises(OverflowError):
         S.pack_requests(bad)
+    # both conversions of the C packer: one-digit ints are read in place, everything else
+    # (two-digit ints, negative values, NumPy integers) takes the general route
+    for value in (0, 1, (1 << 30) - 1, 1 << 30, (1 << 31) - 1, -1, -(1 << 31)):
+        edge = hand_case()
+        edge[1].block_ids = [value, np.int64(value)]      # the prefill request: first after the sort
+        packed, batch = S.pack_requests(edge)[:2]
+        assert packed[4 * batch:4 * batch + 2].tolist() == [value, value]
+    for value in (1 << 31, -(1 << 31) - 1):
+        edge = hand_case()
+        edge[0].block_ids = [value]
+        with pytest.raises(OverflowError):
+            S.pack_requests(edge)
     with pytest.raises(ValueError, match="staging"):
         S.pack_requests(hand_case(), np.zeros(13, dtype=np.int32))
     with pytest.raises(AttributeError):
