@@ -38,6 +38,7 @@ class ModelStepCache:
         self.handle = handle
         self.stream = stream
         self.block_size = int(kv_caches.shape[3])
+        self._layers = list(kv_caches.unbind(0))     # per-layer views, made once
         self.builder = StepInputBuilder(kv_caches.device, self.block_size, max_batch=max_batch,
                                         max_tokens=max_tokens, max_blocks=max_blocks)
 
@@ -67,5 +68,5 @@ class ModelStepCache:
         ``[T, H, D]`` of this step's tokens go to the pages of ``kv_caches[layer]`` that the
         step's page table names.  Runs on the current stream."""
         cache_ops.append_paged_kv_cache(key, value, params.batch_indices, params.positions,
-                                        self.kv_caches[layer], params.kv_block_indices,
+                                        self._layers[layer], params.kv_block_indices,
                                         params.kv_block_indptrs, params.kv_last_block_lens)
