@@ -158,6 +158,28 @@ def test_host_pool_from_existing_buffer():
         HostPool.from_buffer(np.zeros(100, np.uint8), 2, shape.chunk_bytes)
 
 
+def test_host_pool_on_huge_pages_round_trip():
+    """The pool made of transparent huge pages (or of small ones where the kernel grants none)
+    is 2 MiB aligned, starts zeroed and swaps like any other pool, with every engine."""
+    shape = W.SHAPES["llama31_8b_swap"].scaled(num_layers=3, num_blocks=24, num_kv_heads=2)
+    words, gpu = make_gpu_cache(shape, 71)
+    pool = HostPool.with_huge_pages(40, 3, shape.chunk_bytes)
+    try:
+        assert pool.host_ptr % (2 << 20) == 0 and pool.num_blocks == 40
+        assert not pool.array.any()
+        rng = np.random.default_rng(72)
+        out_pairs = np.stack([rng.permutation(24)[:10], rng.permutation(40)[:10]], 1).astype(np.int64)
+        want = np.zeros((40, 3, shape.chunk_bytes // 2), np.uint16)
+        cache_oracle.swap_out(words.reshape(3, 24, -1), want, out_pairs)
+        for engine in ("kernel", "dma", "staged"):
+            pool.array[:] = 0
+            cache_ops.swap_blocks(gpu, pool, out_pairs, "out", engine=engine)
+            torch.cuda.synchronize()
+            assert np.array_equal(pool.array.view(np.uint16), want), engine
+    finally:
+        pool.close()
+
+
 def test_kvworker_copy_kv_with_layer_events():
     """Write-through then fetch, one launch per layer, ordered by per-layer events the way the
     model's forward hooks and the KV worker hand layers to each other."""
