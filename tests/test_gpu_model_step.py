@@ -97,6 +97,48 @@ def test_three_model_steps_with_copy_on_write_and_write_through():
         worker.close()
 
 
+@pytest.mark.parametrize("seed", [11, 12, 13, 14, 15, 16])
+def test_random_step_sequences_match_the_oracles(seed):
+    """Five steps in a row on one cache with a random mix per step (decode only, prefill only,
+    both; with and without copy-on-write): the cached per-layer plans are reused whenever a
+    step has the shape of an earlier one, and the cache must match the oracles after each."""
+    L_, NB, BS, H, D = 4, 160, 16, 2, 32
+    shape = W.KVShape("toy", L_, H, D, "bf16", NB, BS)
+    rng = np.random.default_rng(seed)
+    words = W.normal_words(rng, shape.cache_shape, "bf16")
+    kv = to_tensor(words, "bf16", DEV)
+    want = words.copy()
+    step_cache = ModelStepCache(kv, max_batch=64, max_tokens=1024, max_blocks=2048)
+    layers = [Attention(l, step_cache, H, D) for l in range(L_)]
+    for step in range(5):
+        kind = int(rng.integers(0, 3))
+        n_dec = 0 if kind == 1 else int(rng.integers(1, 20))
+        n_pre = 0 if kind == 0 else int(rng.integers(1, 4))
+        reqs = W.make_step_requests(128, BS, n_dec, 1, 90, n_pre, int(rng.integers(2, 70)), 60,
+                                    seed=seed * 100 + step)
+        ref = step_oracle.make_inputs(copy.deepcopy(reqs), BS)
+        cow = None
+        if rng.integers(0, 2):
+            src = rng.choice(ref["kv_block_indices"], size=2, replace=False)
+            dst = 128 + rng.permutation(32)[:5]
+            cow = {int(src[0]): [int(d) for d in dst[:3]], int(src[1]): [int(d) for d in dst[3:]]}
+        input_ids, params = step_cache.begin_step(reqs, blocks_to_copy=cow)
+        for layer in layers:
+            layer.params = params
+            layer(input_ids)
+        torch.cuda.synchronize()
+        assert np.array_equal(input_ids.cpu().numpy(), ref["input_ids"])
+        if cow:
+            cache_oracle.copy_blocks(want, cow)
+        ids = torch.from_numpy(ref["input_ids"]).to(DEV)
+        for l, layer in enumerate(layers):
+            k, v = layer.kv(ids)
+            cache_oracle.append_paged_kv_cache(to_words(k), to_words(v), ref["batch_indices"],
+                                               ref["positions"], want[l], ref["kv_block_indices"],
+                                               ref["kv_block_indptrs"])
+        assert np.array_equal(to_words(kv), want), f"seed {seed}: cache differs after step {step}"
+
+
 def test_model_step_cache_argument_errors():
     with pytest.raises(ValueError, match="kv_caches must be"):
         ModelStepCache(torch.zeros(2, 4, 16, 2, 8, device=DEV))
