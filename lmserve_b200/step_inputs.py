@@ -87,7 +87,9 @@ def pack_requests(inputs: List, out: Optional[np.ndarray] = None) -> tuple:
     batch = len(inputs)
     if batch > MAX_BATCH:
         raise ValueError(f"at most {MAX_BATCH} requests per step, got {batch}")
-    arrays = batch > 0 and all(isinstance(d.block_ids, np.ndarray) for d in inputs)
+    # block tables kept as NumPy arrays by the caller are concatenated by NumPy; judged by the
+    # first request (either route takes any mix of lists and arrays, this only picks the faster)
+    arrays = batch > 0 and isinstance(inputs[0].block_ids, np.ndarray)
     if _packer is not None and not arrays:
         # one pass in C over the request objects, written straight into `out`
         if out is None:
