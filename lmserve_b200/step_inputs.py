@@ -19,6 +19,7 @@ from __future__ import annotations
 
 from dataclasses import dataclass
 from itertools import chain
+from operator import attrgetter
 from typing import List, Optional, Sequence, Tuple
 
 import numpy as np
@@ -28,6 +29,8 @@ from . import _lib
 from .ops.cache_ops import _OnDevice, _stream_ptr
 
 from .ops.cache_ops import _packer  # the C packer (csrc/packer.c); its absence is an ImportError
+
+_INPUT_LEN = attrgetter("input_len")
 
 MAX_BATCH = 4096  # LMS_STEP_MAX_BATCH
 
@@ -83,7 +86,9 @@ def pack_requests(inputs: List, out: Optional[np.ndarray] = None) -> tuple:
     total_blocks, prefill_input_len, num_prefill, num_decode, prefill_blocks, decode_blocks)``;
     the last two are the block-table entries of the prefill and of the decode requests.
     """
-    inputs.sort(key=lambda x: -x.input_len)
+    # the reference's ``inputs.sort(key=lambda x: -x.input_len)``: a stable descending sort,
+    # written so that the key is read in C
+    inputs.sort(key=_INPUT_LEN, reverse=True)
     batch = len(inputs)
     if batch > MAX_BATCH:
         raise ValueError(f"at most {MAX_BATCH} requests per step, got {batch}")
